@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""Benchmark of the INT4 block-16 GEMV decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the Qwen3-8B-shape per-layer GEMV set at M = 1 -- QKV
+4096->6144, O 4096->4096, gate+up 4096->21888, down 10944->4096, LM head
+4096->151643 -- in the W4A8 format (packed int4 weights, one binary16 scale per
+16-element k-block, binary16 activations quantized to int8 inside the GEMV
+prologue).  One step = one pass over the five matrices = five kernel launches.
+Weights are seeded synthetic (random-init) values with the benchmark's
+distributions; the set is 498 MB, four times the L2, so every pass streams from
+HBM.
+
+The metric is achieved HBM bandwidth: algorithmic bytes (nibbles + weight
+scales + activations + outputs, each counted once) per second over all ranks.
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+from blackwell_b200 import shapes  # noqa: E402
+
+METRIC = "int4_gemv_hbm_gbs"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the ncu capture
+# summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def gemv_set(shape=shapes.QWEN3_8B):
+    return shape.gemv_set()
+
+
+def set_bytes(mats, M=1, x_kind="f16"):
+    return sum(shapes.gemv_bytes(N, K, M, 2, x_kind) for _, N, K in mats)
+
+
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._th = None
+
+    def start(self):
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            self.h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.nv = nv
+            self.max_mhz = int(nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+            return
+        self._th = threading.Thread(target=self._run, daemon=True)
+        self._th.start()
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def stop(self):
+        self._stop.set()
+        if self._th:
+            self._th.join(timeout=1.0)
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------
+def cpu_sample_baseline(threads: int = 0, frac: int = 8, reps: int = 1, seed: int = 900):
+    """Times the oracle's scalar dequant-dot (the host port of the reference kernel) on the first 1/frac of the
+    rows of each of the five matrices.  Returns (GB/s, cores, sample description, seconds)."""
+    import oracle
+    from blackwell_b200 import synth
+
+    mats = gemv_set()
+    work = []
+    for i, (name, N, K) in enumerate(mats):
+        n = max(16, N // frac)
+        W, sc16, _ = synth.int4_weights(n, K, seed + i)
+        x = synth.activations_f16(1, K, seed + 100 + i).astype(np.float32)
+        xq, xs = oracle.quantize_int8(x)
+        work.append((n, K, W, sc16, xq, xs))
+    nbytes = sum(shapes.gemv_bytes(n, K, 1, 2, "f16") for n, K, *_ in work)
+    used = 1
+    for n, K, W, sc16, xq, xs in work:  # warm-up (page-in, thread pool)
+        _, used = oracle.gemv_w4a8_f32(xq, xs, W, sc16, threads)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        for n, K, W, sc16, xq, xs in work:
+            oracle.quantize_int8(np.zeros((1, K), np.float32))  # the activation quantize step of the path
+            oracle.gemv_w4a8_f32(xq, xs, W, sc16, threads)
+    dt = time.perf_counter() - t0
+    gbs = nbytes * reps / dt / 1e9
+    sample = f"first 1/{frac} of the rows of each of the 5 matrices (M=1), {reps} pass(es), {nbytes / 1e6:.1f} MB/pass"
+    return gbs, used, sample, dt
+
+
+def run_reference(args, rank):
+    """Reference arm: the reference has no CPU implementation of this path, so its arithmetic restated on the host
+    (oracle/oracle.c, scalar fp32 dequant-dot, OpenMP over rows) is timed on all host cores."""
+    if rank != 0:
+        return
+    frac = 8
+    # size the step so that warmup + steps stays within a few minutes
+    gbs1, cores, sample, dt = cpu_sample_baseline(0, frac, 1)
+    times = []
+    for _ in range(args.warmup):
+        cpu_sample_baseline(0, frac, 1)
+    for _ in range(args.steps):
+        g, cores, sample, dt = cpu_sample_baseline(0, frac, 1)
+        times.append(dt)
+    mats = gemv_set()
+    nbytes = sum(shapes.gemv_bytes(max(16, N // frac), K, 1, 2, "f16") for _, N, K in mats)
+    t = float(np.mean(times))
+    val = nbytes / t / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8xint4->int32, fp32 scale", "data": "synthetic",
+        "config": {"workload": "qwen3-8b-shape per-layer GEMV set, M=1, W4A8 block-16 (configs[1])",
+                   "matrices": [[n, N, K] for n, N, K in mats]},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    from blackwell_b200 import kernels as k
+    from blackwell_b200 import synth, tp
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    mats = gemv_set()
+    M = 1
+    plan = tp.shard_gemv_set(mats, world, rank)
+
+    # resident state: this rank's shard of the five matrices, activations, outputs
+    state = []
+    for i, sh in enumerate(plan):
+        W, sc = synth.int4_weights_device(sh.n_local, sh.k_local, 500 + 17 * i + rank, device=dev)
+        x = synth.activations_f16_device(M, sh.k_local, 600 + i, device=dev)
+        y = torch.empty((M, sh.n_local), dtype=torch.float32, device=dev)
+        state.append((sh, W, sc, x, y))
+    coll = tp.Collectives(world, rank, dev) if world > 1 else None
+
+    def step():
+        for sh, W, sc, x, y in state:
+            k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
+            if coll is not None:
+                coll.finish(sh, y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    k.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = k.launch_count()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        tmax = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms = float(tmax.item())
+    assert k.device_status() == 0, "a kernel reported a bounded-wait timeout"
+    total_bytes = set_bytes(mats, M)  # whole job: the full matrices, whatever the sharding
+    sec_per_step = ms / 1e3 / args.steps
+    value = total_bytes / sec_per_step / 1e9
+
+    # ---- end to end through the public call with host buffers (pinned), copies inside the timed region
+    host_x = [torch.empty((M, sh.k_local), dtype=torch.float16).pin_memory() for sh, *_ in state]
+    for hx, (_, _, _, x, _) in zip(host_x, state):
+        hx.copy_(x.cpu())
+    host_y = [torch.empty((M, sh.n_local), dtype=torch.float32).pin_memory() for sh, *_ in state]
+    h2d = sum(h.numel() * 2 for h in host_x)
+    d2h = sum(h.numel() * 4 for h in host_y)
+
+    def e2e_step():
+        for hx, hy, (sh, W, sc, x, y) in zip(host_x, host_y, state):
+            x.copy_(hx, non_blocking=True)
+            k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
+            if coll is not None:
+                coll.finish(sh, y)
+            hy.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_sec = (time.perf_counter() - t0) / args.steps
+    if world > 1:
+        tmax = torch.tensor([e2e_sec], dtype=torch.float64, device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        e2e_sec = float(tmax.item())
+    e2e_val = total_bytes / e2e_sec / 1e9
+
+    # ---- per-matrix launch durations (CUDA events around each launch, same stream), L2 flushed by the
+    # other matrices of the set between two launches of the same matrix
+    per = []
+    if rank == 0:
+        evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in state]
+               for _ in range(10)]
+        for rep in evs:
+            for (a, b), (sh, W, sc, x, y) in zip(rep, state):
+                a.record()
+                k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
+                b.record()
+        torch.cuda.synchronize()
+        peak, _ = measured_peak()
+        for i, (sh, *_rest) in enumerate(state):
+            us = float(np.median([rep[i][0].elapsed_time(rep[i][1]) for rep in evs])) * 1e3
+            b = shapes.gemv_bytes(sh.n_local, sh.k_local, M, 2, "f16")
+            per.append({"name": sh.name, "N": sh.n_local, "K": sh.k_local, "us": round(us, 2),
+                        "gbs": round(b / us / 1e3, 1), "frac": round(b / us / 1e3 / peak, 3)})
+    if world > 1:
+        barrier()
+
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak()
+    # dominant kernel: gemv_w4_stream_kernel<1, half>; every launch in the timed region is one of its launches
+    n_launch = launches / args.steps
+    per_launch_bytes = total_bytes / world / max(n_launch, 1)
+    per_launch_s = sec_per_step / max(n_launch, 1)
+    achieved = per_launch_bytes / per_launch_s / 1e9
+    cpu = None
+    if world == 1:
+        g, cores, sample, _ = cpu_sample_baseline(0, 8, 2)
+        cpu = {"value": g, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8xint4->int32, fp32 scale", "data": "synthetic",
+        "config": {"workload": "qwen3-8b-shape per-layer GEMV set, M=1, W4A8 block-16 (configs[1])",
+                   "matrices": [[n, N, K] for n, N, K in mats], "bytes_per_step": total_bytes,
+                   "l2": "inputs larger than L2 (498 MB set, 126 MB L2)",
+                   "parallelism": "tp%d" % world if world > 1 else "single"},
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind,
+                     "kernel": "gemv_w4_stream_kernel<1,half>", "nominal_frac": achieved / 8000.0},
+        "cpu_baseline": cpu,
+        "per_matrix": per,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,330 @@
+// GQA decode attention (one new token per sequence) and KV-cache update.
+//
+// Cache layout (caller's): element type f32 (reference format) or binary16
+// (extension), addressed as
+//   base + m * kv_batch_elems + kv_layer_elems + kv_head * max_seq * 128 + t * 128.
+//
+// Flash-decoding structure: the context of every (sequence, kv head) is cut
+// into splits so that the grid fills the GPU at small batch; a CTA streams its
+// K and V rows once and serves all the query heads that share the kv head
+// (GQA), keeping an online-softmax state per head; per-split partial results
+// go to a scratch buffer and a second small kernel merges them.  head_dim is
+// 128 (32 lanes x 4 elements).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+
+#include <mutex>
+
+#include "../../include/blackwell_b200.h"
+#include "common.cuh"
+#include "host_util.h"
+
+namespace bw {
+
+constexpr int kHd = 128;
+constexpr int kAttnWarps = 4;
+constexpr int kPosPerStep = 4;  // positions handled together by one warp
+
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __half* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+struct AttnArgs {
+    float* out;            // [M][nqh][128]
+    const float* Q;        // [M][nqh][128]
+    const void* K;
+    const void* V;
+    const int* d_seq_pos;  // device positions (shared or per sequence) or nullptr
+    int seq_pos;           // host value when d_seq_pos == nullptr
+    int per_seq;           // d_seq_pos has M entries
+    int nqh, nkv, max_seq, M;
+    size_t kv_batch_elems, kv_layer_elems;
+    int nsplit, split_len;
+    float scale;
+    float* part;           // [M][nqh][nsplit][130] when nsplit > 1
+};
+
+// Partial record of one (sequence, head, split): 128 un-normalised outputs, then max and sum.
+constexpr int kPartStride = kHd + 2;
+
+template <typename KVT, int GQ>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_split_kernel(const AttnArgs a) {
+    const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int seq_pos = a.d_seq_pos ? a.d_seq_pos[a.per_seq ? m : 0] : a.seq_pos;
+    const int npos = min(seq_pos + 1, a.max_seq);
+    const int p0 = split * a.split_len;
+    const int p1 = min(npos, p0 + a.split_len);
+
+    const KVT* Kb = static_cast<const KVT*>(a.K) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
+                    (size_t)kvh * a.max_seq * kHd;
+    const KVT* Vb = static_cast<const KVT*>(a.V) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
+                    (size_t)kvh * a.max_seq * kHd;
+    const int h0 = kvh * GQ;  // first query head of the group (head * nkv / nqh == kvh)
+
+    __shared__ float s_scores[kAttnWarps][kPosPerStep * GQ];
+    __shared__ float s_m[kAttnWarps][GQ], s_l[kAttnWarps][GQ];
+    __shared__ float s_o[kAttnWarps][GQ][kHd];
+
+    float4 q[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; ++h) {
+        q[h] = load4(a.Q + ((size_t)m * a.nqh + h0 + h) * kHd + 4 * lane);
+        q[h].x *= a.scale; q[h].y *= a.scale; q[h].z *= a.scale; q[h].w *= a.scale;
+    }
+    float mx[GQ], l[GQ];
+    float4 o[GQ];
+#pragma unroll
+    for (int h = 0; h < GQ; ++h) {
+        mx[h] = -FLT_MAX; l[h] = 0.f; o[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+
+    for (int tb = p0 + warp * kPosPerStep; tb < p1; tb += kAttnWarps * kPosPerStep) {
+        float4 kr[kPosPerStep], vr[kPosPerStep];
+#pragma unroll
+        for (int j = 0; j < kPosPerStep; ++j) {
+            const int tt = min(tb + j, p1 - 1);  // clamped rows are masked below
+            kr[j] = load4(Kb + (size_t)tt * kHd + 4 * lane);
+            vr[j] = load4(Vb + (size_t)tt * kHd + 4 * lane);
+        }
+        float partial[kPosPerStep * GQ];
+#pragma unroll
+        for (int j = 0; j < kPosPerStep; ++j)
+#pragma unroll
+            for (int h = 0; h < GQ; ++h)
+                partial[j * GQ + h] = q[h].x * kr[j].x + q[h].y * kr[j].y + q[h].z * kr[j].z + q[h].w * kr[j].w;
+        const float tot = warp_sum_many<kPosPerStep * GQ>(partial, lane);
+        constexpr int V = kPosPerStep * GQ;  // 4, 8, 16 or 32: already a power of two
+        if ((lane & (32 / V - 1)) == 0) s_scores[warp][warp_sum_many_index<V>(lane)] = tot;
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < GQ; ++h) {
+            float s[kPosPerStep];
+            float mnew = mx[h];
+#pragma unroll
+            for (int j = 0; j < kPosPerStep; ++j) {
+                s[j] = (tb + j < p1) ? s_scores[warp][j * GQ + h] : -FLT_MAX;
+                mnew = fmaxf(mnew, s[j]);
+            }
+            const float corr = __expf(mx[h] - mnew);
+            float psum = 0.f;
+            float4 acc = make_float4(o[h].x * corr, o[h].y * corr, o[h].z * corr, o[h].w * corr);
+#pragma unroll
+            for (int j = 0; j < kPosPerStep; ++j) {
+                const float p = (tb + j < p1) ? __expf(s[j] - mnew) : 0.f;
+                psum += p;
+                acc.x = fmaf(p, vr[j].x, acc.x); acc.y = fmaf(p, vr[j].y, acc.y);
+                acc.z = fmaf(p, vr[j].z, acc.z); acc.w = fmaf(p, vr[j].w, acc.w);
+            }
+            o[h] = acc;
+            l[h] = l[h] * corr + psum;
+            mx[h] = mnew;
+        }
+        __syncwarp();
+    }
+
+    // merge the four warps
+#pragma unroll
+    for (int h = 0; h < GQ; ++h) {
+        if (lane == 0) { s_m[warp][h] = mx[h]; s_l[warp][h] = l[h]; }
+        *reinterpret_cast<float4*>(&s_o[warp][h][4 * lane]) = o[h];
+    }
+    __syncthreads();
+    for (int idx = t; idx < GQ * kHd; idx += blockDim.x) {
+        const int h = idx / kHd, d = idx - h * kHd;
+        float mm = -FLT_MAX;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, s_m[w][h]);
+        float ls = 0.f, os = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float c = __expf(s_m[w][h] - mm);
+            ls = fmaf(s_l[w][h], c, ls);
+            os = fmaf(s_o[w][h][d], c, os);
+        }
+        const size_t head = (size_t)m * a.nqh + h0 + h;
+        if (a.nsplit == 1) {
+            a.out[head * kHd + d] = os * (1.0f / (ls + 1e-9f));
+        } else {
+            float* rec = a.part + (head * a.nsplit + split) * kPartStride;
+            rec[d] = os;
+            if (d == 0) { rec[kHd] = mm; rec[kHd + 1] = ls; }
+        }
+    }
+}
+
+// Merges the per-split partial records of one (sequence, head).
+__global__ void __launch_bounds__(kHd) attn_merge_kernel(float* out, const float* part, int nsplit) {
+    const size_t head = blockIdx.x;
+    const int d = threadIdx.x;
+    const float* rec = part + head * nsplit * kPartStride;
+    float mm = -FLT_MAX;
+    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, rec[s * kPartStride + kHd]);
+    float ls = 0.f, os = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float lsp = rec[s * kPartStride + kHd + 1];
+        if (lsp > 0.f) {
+            const float c = __expf(rec[s * kPartStride + kHd] - mm);
+            ls = fmaf(lsp, c, ls);
+            os = fmaf(rec[s * kPartStride + d], c, os);
+        }
+    }
+    out[head * kHd + d] = os * (1.0f / (ls + 1e-9f));
+}
+
+// Scatter of the new K and V rows into the cache [head][max_seq][head_dim] at
+// the position given by value or read from device memory.
+template <typename KVT>
+__global__ void __launch_bounds__(256) update_kv_kernel_b200(KVT* kc, KVT* vc, const float* k_new,
+                                                             const float* v_new, const int* d_pos, int pos_value,
+                                                             int nh, int hd, int max_seq) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= nh * hd) return;
+    const int pos = d_pos ? *d_pos : pos_value;
+    const int h = idx / hd, d = idx - h * hd;
+    const size_t off = (size_t)h * max_seq * hd + (size_t)pos * hd + d;
+    kc[off] = (KVT)k_new[idx];
+    vc[off] = (KVT)v_new[idx];
+}
+
+// ------------------------------------------------------------------ host side
+struct Scratch {
+    float* ptr = nullptr;
+    size_t bytes = 0;
+};
+static Scratch g_scratch[kMaxDevices];
+static std::mutex g_scratch_mu;
+
+// Grow-only per-device scratch for the split partials.  Growing frees and
+// reallocates (synchronising); it happens on the first call and when a larger
+// problem arrives, never in steady state.
+static cudaError_t attn_scratch(size_t bytes, float** out) {
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    Scratch& s = g_scratch[current_device()];
+    if (s.bytes < bytes) {
+        if (s.ptr) cudaFree(s.ptr);
+        s.ptr = nullptr; s.bytes = 0;
+        size_t want = bytes < (size_t)(4 << 20) ? (size_t)(4 << 20) : bytes;
+        cudaError_t e = cudaMalloc(&s.ptr, want);
+        if (e != cudaSuccess) return e;
+        s.bytes = want;
+    }
+    *out = s.ptr;
+    return cudaSuccess;
+}
+
+template <typename KVT>
+static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
+    if (!a.out || !a.Q || !a.K || !a.V || a.nqh < 1 || a.nkv < 1 || a.nqh % a.nkv != 0 || a.M < 1 || a.max_seq < 1)
+        return cudaErrorInvalidValue;
+    const int gq = a.nqh / a.nkv;
+    if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return cudaErrorInvalidValue;
+    if (ctx_hint < 1) ctx_hint = 1;
+    if (ctx_hint > a.max_seq) ctx_hint = a.max_seq;
+    // enough CTAs for ~2 per SM, at least 64 positions per split
+    const int sms = sm_count(current_device());
+    int nsplit = (2 * sms + a.M * a.nkv - 1) / (a.M * a.nkv);
+    const int max_split = (ctx_hint + 63) / 64;
+    if (nsplit > max_split) nsplit = max_split;
+    if (nsplit > 64) nsplit = 64;
+    if (nsplit < 1) nsplit = 1;
+    a.split_len = (ctx_hint + nsplit - 1) / nsplit;
+    a.split_len = (a.split_len + kPosPerStep - 1) / kPosPerStep * kPosPerStep;
+    nsplit = (ctx_hint + a.split_len - 1) / a.split_len;
+    a.nsplit = nsplit;
+    a.scale = 1.0f / sqrtf((float)kHd);
+    a.part = nullptr;
+    if (nsplit > 1) {
+        cudaError_t e = attn_scratch((size_t)a.M * a.nqh * nsplit * kPartStride * sizeof(float), &a.part);
+        if (e != cudaSuccess) return e;
+    }
+    const dim3 grid(nsplit, a.nkv, a.M);
+    switch (gq) {
+        case 1: attn_decode_split_kernel<KVT, 1><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+        case 2: attn_decode_split_kernel<KVT, 2><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+        case 4: attn_decode_split_kernel<KVT, 4><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+        default: attn_decode_split_kernel<KVT, 8><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+    }
+    count_launch(1);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return e;
+    if (nsplit > 1) {
+        attn_merge_kernel<<<a.M * a.nqh, kHd, 0, st>>>(a.out, a.part, nsplit);
+        count_launch(1);
+        e = cudaPeekAtLastError();
+    }
+    return e;
+}
+
+}  // namespace bw
+
+using namespace bw;
+
+extern "C" int bw_attention_decode_batched_gqa(float* output, const float* Q, const float* K_cache,
+                                               const float* V_cache, int seq_pos, int num_q_heads, int num_kv_heads,
+                                               int head_dim, int max_seq_len, int M, size_t kv_batch_elems,
+                                               size_t kv_layer_elems, void* stream) {
+    if (head_dim != kHd || seq_pos < 0 || seq_pos >= max_seq_len) return cudaErrorInvalidValue;
+    AttnArgs a{};
+    a.out = output; a.Q = Q; a.K = K_cache; a.V = V_cache; a.d_seq_pos = nullptr; a.seq_pos = seq_pos; a.per_seq = 0;
+    a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
+    a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
+    return attn_launch<float>(a, seq_pos + 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_attention_decode_batched_gqa_device(float* output, const float* Q, const float* K_cache,
+                                                      const float* V_cache, const int* d_seq_pos, int num_q_heads,
+                                                      int num_kv_heads, int head_dim, int max_seq_len, int M,
+                                                      size_t kv_batch_elems, size_t kv_layer_elems, void* stream) {
+    if (head_dim != kHd || !d_seq_pos) return cudaErrorInvalidValue;
+    AttnArgs a{};
+    a.out = output; a.Q = Q; a.K = K_cache; a.V = V_cache; a.d_seq_pos = d_seq_pos; a.per_seq = 0;
+    a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
+    a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
+    return attn_launch<float>(a, max_seq_len, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_attention_decode_f16kv(float* output, const float* Q, const uint16_t* K_cache,
+                                         const uint16_t* V_cache, const int* d_seq_pos, int ctx_hint, int num_q_heads,
+                                         int num_kv_heads, int head_dim, int max_seq_len, int M,
+                                         size_t kv_batch_elems, size_t kv_layer_elems, void* stream) {
+    if (head_dim != kHd || !d_seq_pos) return cudaErrorInvalidValue;
+    AttnArgs a{};
+    a.out = output; a.Q = Q; a.K = K_cache; a.V = V_cache; a.d_seq_pos = d_seq_pos; a.per_seq = 1;
+    a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
+    a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
+    return attn_launch<__half>(a, ctx_hint > 0 ? ctx_hint : max_seq_len, static_cast<cudaStream_t>(stream));
+}
+
+static int update_kv_impl(float* k_cache, float* v_cache, const float* k_new, const float* v_new, int batch_idx,
+                          const int* d_pos, int pos, int num_heads, int head_dim, int max_seq_len, void* stream) {
+    if (!k_cache || !v_cache || !k_new || !v_new || num_heads < 1 || head_dim < 1 || max_seq_len < 1)
+        return cudaErrorInvalidValue;
+    if (batch_idx != 0) return cudaErrorInvalidValue;  // same contract as the reference
+    if (!d_pos && (pos < 0 || pos >= max_seq_len)) return cudaErrorInvalidValue;
+    const int total = num_heads * head_dim;
+    update_kv_kernel_b200<float><<<(total + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        k_cache, v_cache, k_new, v_new, d_pos, pos, num_heads, head_dim, max_seq_len);
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+extern "C" int bw_update_kv_cache(float* k_cache, float* v_cache, const float* k_new, const float* v_new,
+                                  int batch_idx, int seq_pos, int num_heads, int head_dim, int max_seq_len,
+                                  void* stream) {
+    return update_kv_impl(k_cache, v_cache, k_new, v_new, batch_idx, nullptr, seq_pos, num_heads, head_dim,
+                          max_seq_len, stream);
+}
+
+extern "C" int bw_update_kv_cache_device(float* k_cache, float* v_cache, const float* k_new, const float* v_new,
+                                         int batch_idx, const int* d_seq_pos, int num_heads, int head_dim,
+                                         int max_seq_len, void* stream) {
+    if (!d_seq_pos) return cudaErrorInvalidValue;
+    return update_kv_impl(k_cache, v_cache, k_new, v_new, batch_idx, d_seq_pos, 0, num_heads, head_dim, max_seq_len,
+                          stream);
+}

@@ -1,0 +1,363 @@
+// Host dispatch and C entry points of the INT4 block-16 GEMV family, plus the
+// plain-load kernel used for ragged tails / unaligned operands / M > 8 and the
+// per-block integer dot product inspection kernel.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "../../include/blackwell_b200.h"
+#include "gemv_w4_stream.cuh"
+#include "host_util.h"
+
+namespace bw {
+
+// --------------------------------------------------------------------------
+// Plain-load kernel: one warp per output row, lanes stride over k-blocks, up to
+// 8 sequences per pass.  Any K % 16 == 0, any N, 8-byte aligned weights.  Same
+// integer arithmetic as the streaming kernel (same helpers).
+// --------------------------------------------------------------------------
+template <int M, typename WS>
+__global__ void __launch_bounds__(128) gemv_w4_rows_kernel(const GemvArgs a, int row0, int row_count) {
+    const int lane = threadIdx.x & 31;
+    const int row = row0 + blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= row0 + row_count) return;
+    const int K = a.K, nkb = K / 16;
+
+    float rstd[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) rstd[m] = 1.f;
+    if (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float* xr = static_cast<const float*>(a.x) + (size_t)m * K;
+            float ss = 0.f;
+            for (int i = lane; i < K; i += 32) ss = fmaf(xr[i], xr[i], ss);
+            ss = warp_sum(ss);
+            rstd[m] = rsqrtf(ss / (float)K + a.eps);
+        }
+    }
+
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    const uint2* wrow = reinterpret_cast<const uint2*>(a.W + (size_t)row * (K / 2));
+    const WS* srow = static_cast<const WS*>(a.Wsc) + (size_t)row * nkb;
+    for (int kb = lane; kb < nkb; kb += 32) {
+        const uint2 w = __ldg(wrow + kb);
+        const float ws = (float)srow[kb];
+        uint32_t lo0, hi0, lo1, hi1;
+        nibbles_to_s8x16(w.x, lo0, hi0);
+        nibbles_to_s8x16(w.y, lo1, hi1);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            uint32_t e[2], o[2];
+            float s;
+            make_xblock(a, m, kb, rstd[m], e, o, s);
+            int d = kMagicInt;
+            d = dp4a_ss(lo0, e[0], d);
+            d = dp4a_ss(hi0, o[0], d);
+            d = dp4a_ss(lo1, e[1], d);
+            d = dp4a_ss(hi1, o[1], d);
+            acc[m] = fmaf(__int_as_float(d) - kMagicFloat, ws * s, acc[m]);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const float tot = warp_sum(acc[m]);
+        if (lane == 0) a.y[(size_t)m * a.N + row] = tot;
+    }
+}
+
+// Per-block integer dots of one sequence: dots[n][kb].  x is int8 [K] or
+// INT4-packed [K/2]; scales play no part.
+__global__ void __launch_bounds__(128) block_dots_kernel(int32_t* dots, const uint8_t* W, const void* x, int a8,
+                                                         int K, int N) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const int nkb = K / 16;
+    const uint2* wrow = reinterpret_cast<const uint2*>(W + (size_t)row * (K / 2));
+    for (int kb = lane; kb < nkb; kb += 32) {
+        const uint2 w = __ldg(wrow + kb);
+        uint32_t lo0, hi0, lo1, hi1, e0, o0, e1, o1;
+        nibbles_to_s8x16(w.x, lo0, hi0);
+        nibbles_to_s8x16(w.y, lo1, hi1);
+        if (a8) {
+            const uint2* p = reinterpret_cast<const uint2*>(static_cast<const int8_t*>(x) + 16 * (size_t)kb);
+            const uint2 q0 = __ldg(p), q1 = __ldg(p + 1);
+            e0 = prmt(q0.x, q0.y, 0x6420); o0 = prmt(q0.x, q0.y, 0x7531);
+            e1 = prmt(q1.x, q1.y, 0x6420); o1 = prmt(q1.x, q1.y, 0x7531);
+        } else {
+            const uint2 q = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(x) + 8 * (size_t)kb));
+            e0 = bytes_minus8(q.x & 0x0F0F0F0Fu); o0 = bytes_minus8((q.x >> 4) & 0x0F0F0F0Fu);
+            e1 = bytes_minus8(q.y & 0x0F0F0F0Fu); o1 = bytes_minus8((q.y >> 4) & 0x0F0F0F0Fu);
+        }
+        int d = kMagicInt;
+        d = dp4a_ss(lo0, e0, d);
+        d = dp4a_ss(hi0, o0, d);
+        d = dp4a_ss(lo1, e1, d);
+        d = dp4a_ss(hi1, o1, d);
+        // the accumulated value is 16 * dot on top of the float bit pattern
+        dots[(size_t)row * nkb + kb] = (int)(__int_as_float(d) - kMagicFloat) / 16;
+    }
+}
+
+// --------------------------------------------------------------------------
+// Host side
+// --------------------------------------------------------------------------
+static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0};
+static std::atomic<long long> g_launches{0};
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+struct StreamPlan {
+    bool ok = false;
+    int Tg = 0, G = 0, J = 0, S = 0, T = 0, row_unit = 1, n_rows = 0, grid = 0;
+    size_t smem = 0;
+};
+
+template <int M, typename WS, bool kMulti>
+static cudaError_t launch_stream_inst(const GemvArgs& a, const StreamPlan& p, cudaStream_t st) {
+    auto kern = gemv_w4_stream_kernel<M, WS, kMulti>;
+    static std::once_flag once[kMaxDevices];
+    const int dev = current_device();
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(once[dev], [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem);
+    });
+    if (attr_err != cudaSuccess) return attr_err;
+    int occ = 1;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, p.T, p.smem);
+    if (e != cudaSuccess) return e;
+    if (occ < 1) return cudaErrorInvalidConfiguration;
+    const int cap = g_tune_ctas.load();
+    if (cap > 0 && occ > cap) occ = cap;
+    const int units = p.n_rows / p.row_unit;
+    int grid = sm_count(dev) * occ;
+    if (grid > units) grid = units;
+    kern<<<grid, p.T, p.smem, st>>>(a);
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+template <int M, typename WS>
+static cudaError_t launch_stream_m(const GemvArgs& a, const StreamPlan& p, cudaStream_t st) {
+    return p.J > 1 ? launch_stream_inst<M, WS, true>(a, p, st) : launch_stream_inst<M, WS, false>(a, p, st);
+}
+
+template <typename WS>
+static cudaError_t launch_stream(const GemvArgs& a, const StreamPlan& p, int M, cudaStream_t st) {
+    switch (M) {
+        case 1: return launch_stream_m<1, WS>(a, p, st);
+        case 2: return launch_stream_m<2, WS>(a, p, st);
+        case 3: return launch_stream_m<3, WS>(a, p, st);
+        case 4: return launch_stream_m<4, WS>(a, p, st);
+        case 5: return launch_stream_m<5, WS>(a, p, st);
+        case 6: return launch_stream_m<6, WS>(a, p, st);
+        case 7: return launch_stream_m<7, WS>(a, p, st);
+        case 8: return launch_stream_m<8, WS>(a, p, st);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+template <typename WS>
+static cudaError_t launch_rows(const GemvArgs& a, int M, int row0, int row_count, cudaStream_t st) {
+    if (row_count <= 0) return cudaSuccess;
+    const int wpb = 4;
+    const int grid = (row_count + wpb - 1) / wpb;
+    switch (M) {
+        case 1: gemv_w4_rows_kernel<1, WS><<<grid, 32 * wpb, 0, st>>>(a, row0, row_count); break;
+        case 2: gemv_w4_rows_kernel<2, WS><<<grid, 32 * wpb, 0, st>>>(a, row0, row_count); break;
+        case 3: gemv_w4_rows_kernel<3, WS><<<grid, 32 * wpb, 0, st>>>(a, row0, row_count); break;
+        case 4: gemv_w4_rows_kernel<4, WS><<<grid, 32 * wpb, 0, st>>>(a, row0, row_count); break;
+        case 5: gemv_w4_rows_kernel<5, WS><<<grid, 32 * wpb, 0, st>>>(a, row0, row_count); break;
+        case 6: gemv_w4_rows_kernel<6, WS><<<grid, 32 * wpb, 0, st>>>(a, row0, row_count); break;
+        case 7: gemv_w4_rows_kernel<7, WS><<<grid, 32 * wpb, 0, st>>>(a, row0, row_count); break;
+        case 8: gemv_w4_rows_kernel<8, WS><<<grid, 32 * wpb, 0, st>>>(a, row0, row_count); break;
+        default: return cudaErrorInvalidValue;
+    }
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+static inline bool aligned(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
+
+// Decides whether the streaming kernel can take the launch and with what shape.
+static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
+    StreamPlan p;
+    const int K = a.K, N = a.N;
+    if (g_tune_force_plain.load() || M < 1 || M > 8 || K % 32 != 0 || N < 1) return p;
+    if (!aligned(a.W, 16) || !aligned(a.Wsc, 16) || !aligned(a.x, 16)) return p;
+    if (a.xsc && !aligned(a.xsc, 8)) return p;
+    if (a.x2 && !aligned(a.x2, 16)) return p;
+    if (a.norm_w && !aligned(a.norm_w, 16)) return p;
+    const int nch = K / 32;
+    const int tmax = M <= 2 ? 512 : 256;
+    p.J = (nch + tmax - 1) / tmax;
+    p.Tg = (((nch + p.J - 1) / p.J) + 31) / 32 * 32;
+    p.G = 256 / p.Tg;
+    if (p.G < 1) p.G = 1;
+    p.T = p.Tg * p.G;
+    const int RG = M <= 2 ? 8 : (M <= 4 ? 4 : 2);
+    const int R = RG * p.G;
+    const size_t row_nib = (size_t)K / 2, row_sc = (size_t)(K / 16) * ws_bytes;
+    const size_t stage = align128(R * row_nib) + align128(R * row_sc);
+    const size_t fixed = GemvSmem::kXOff + align128(gemv_x_smem_bytes(M, nch, p.J));
+    if (fixed + 2 * stage > (size_t)kMaxDynSmem) return p;
+    int S = (int)(((size_t)kMaxDynSmem - fixed) / stage);
+    int want = g_tune_stages.load();
+    if (want <= 0) {
+        // keep at least ~64 KB of weights in flight per CTA, leave room for 2 CTAs per SM when cheap
+        want = (int)((65536 + stage - 1) / stage);
+        if (want < 3) want = 3;
+    }
+    if (S > want) S = want;
+    if (S > 8) S = 8;
+    if (S < 2) return p;
+    p.S = S;
+    p.smem = fixed + (size_t)S * stage;
+    p.row_unit = 1;
+    while ((p.row_unit * row_sc) % 16 != 0) p.row_unit *= 2;
+    p.n_rows = N - N % p.row_unit;
+    p.ok = p.n_rows > 0;
+    return p;
+}
+
+template <typename WS>
+static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
+    if (a.K <= 0 || a.K % 16 != 0 || a.N < 1 || M < 1) return cudaErrorInvalidValue;
+    if (!a.y || !a.W || !a.Wsc || !a.x) return cudaErrorInvalidValue;
+    if (!aligned(a.W, 8) || !aligned(a.x, 8)) return cudaErrorInvalidValue;
+    const bool prequant = (a.xkind == kXInt8 || a.xkind == kXInt4);
+    if (!prequant && (M > 8 || !aligned(a.x, 16))) return cudaErrorInvalidValue;
+    a.nch = a.K / 32;
+    // M > 8: passes of up to 8 sequences (pre-quantized operands only).
+    for (int m0 = 0; m0 < M; m0 += 8) {
+        const int mc = (M - m0) < 8 ? (M - m0) : 8;
+        GemvArgs b = a;
+        b.y = a.y + (size_t)m0 * a.N;
+        if (a.xkind == kXInt8) b.x = static_cast<const int8_t*>(a.x) + (size_t)m0 * a.K;
+        if (a.xkind == kXInt4) b.x = static_cast<const uint8_t*>(a.x) + (size_t)m0 * (a.K / 2);
+        if (a.xsc) b.xsc = a.xsc + (size_t)m0 * (a.K / 16);
+        const StreamPlan p = plan_stream(b, mc, (int)sizeof(WS));
+        int done = 0;
+        if (p.ok) {
+            b.Tg = p.Tg; b.G = p.G; b.J = p.J; b.S = p.S;
+            b.row_unit = p.row_unit; b.n_rows = p.n_rows;
+            cudaError_t e = launch_stream<WS>(b, p, mc, st);
+            if (e != cudaSuccess) return e;
+            done = p.n_rows;
+        }
+        cudaError_t e = launch_rows<WS>(b, mc, done, a.N - done, st);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace bw
+
+// ----------------------------------------------------------------------------
+// C entry points
+// ----------------------------------------------------------------------------
+using namespace bw;
+
+extern "C" int bw_gemv_int4_batched(float* y_out, const uint8_t* x_packed, const float* x_scale,
+                                    const uint8_t* W_packed, const float* W_scale, int K, int N, int M,
+                                    void* stream) {
+    GemvArgs a{};
+    a.y = y_out; a.W = W_packed; a.Wsc = W_scale; a.x = x_packed; a.xsc = x_scale;
+    a.xkind = kXInt4; a.K = K; a.N = N;
+    if (!x_scale) return cudaErrorInvalidValue;
+    return gemv_dispatch<float>(a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_gemv_int4_warp(float* y_out, const void* x_packed, const float* x_scale, const void* W_packed,
+                                 const float* W_scale, int K, int N, void* stream) {
+    return bw_gemv_int4_batched(y_out, static_cast<const uint8_t*>(x_packed), x_scale,
+                                static_cast<const uint8_t*>(W_packed), W_scale, K, N, 1, stream);
+}
+
+extern "C" int bw_gemv_w4a8(float* y_out, const int8_t* x_q, const float* x_scale, const uint8_t* W_packed,
+                            const uint16_t* W_scale_f16, int K, int N, int M, void* stream) {
+    GemvArgs a{};
+    a.y = y_out; a.W = W_packed; a.Wsc = W_scale_f16; a.x = x_q; a.xsc = x_scale;
+    a.xkind = kXInt8; a.K = K; a.N = N;
+    if (!x_scale) return cudaErrorInvalidValue;
+    return gemv_dispatch<__half>(a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_gemv_w4a8_f16in(float* y_out, const uint16_t* x_f16, const uint8_t* W_packed,
+                                  const uint16_t* W_scale_f16, int K, int N, int M, void* stream) {
+    GemvArgs a{};
+    a.y = y_out; a.W = W_packed; a.Wsc = W_scale_f16; a.x = x_f16;
+    a.xkind = kXHalf; a.K = K; a.N = N;
+    return gemv_dispatch<__half>(a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_gemv_w4a8_f32in(float* y_out, const float* x_f32, const float* norm_weight, float eps,
+                                  const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N, int M,
+                                  void* stream) {
+    GemvArgs a{};
+    a.y = y_out; a.W = W_packed; a.Wsc = W_scale_f16; a.x = x_f32; a.norm_w = norm_weight; a.eps = eps;
+    a.xkind = norm_weight ? kXFloatNorm : kXFloat; a.K = K; a.N = N;
+    return gemv_dispatch<__half>(a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_gemv_w4a8_swiglu(float* y_out, const float* gate, const float* up, const uint8_t* W_packed,
+                                   const uint16_t* W_scale_f16, int K, int N, int M, void* stream) {
+    if (!up) return cudaErrorInvalidValue;
+    GemvArgs a{};
+    a.y = y_out; a.W = W_packed; a.Wsc = W_scale_f16; a.x = gate; a.x2 = up;
+    a.xkind = kXSwiglu; a.K = K; a.N = N;
+    return gemv_dispatch<__half>(a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_gemv_int4_fused(float* y_out, const float* x_f32, const float* up_or_null,
+                                  const float* norm_weight_or_null, float eps, const uint8_t* W_packed,
+                                  const float* W_scale, int K, int N, int M, void* stream) {
+    if (up_or_null && norm_weight_or_null) return cudaErrorInvalidValue;
+    GemvArgs a{};
+    a.y = y_out; a.W = W_packed; a.Wsc = W_scale; a.x = x_f32; a.x2 = up_or_null; a.norm_w = norm_weight_or_null;
+    a.eps = eps;
+    a.xkind = up_or_null ? kXSwigluI4 : (norm_weight_or_null ? kXFloatNormI4 : kXFloatI4);
+    a.K = K; a.N = N;
+    return gemv_dispatch<float>(a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_gemv_block_dots(int32_t* dots, const void* x, int a8, const uint8_t* W_packed, int K, int N,
+                                  void* stream) {
+    if (!dots || !x || !W_packed || K <= 0 || K % 16 != 0 || N < 1) return cudaErrorInvalidValue;
+    if (!aligned(W_packed, 8) || !aligned(x, 8)) return cudaErrorInvalidValue;
+    block_dots_kernel<<<(N + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(dots, W_packed, x, a8, K, N);
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+extern "C" int bw_device_status(int* status_out) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
+    if (e != cudaSuccess) return e;
+    if (v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+    }
+    if (status_out) *status_out = v;
+    return e;
+}
+
+extern "C" int bw_set_tuning(int key, int value) {
+    switch (key) {
+        case 0: g_tune_stages = value; return 0;
+        case 1: g_tune_ctas = value; return 0;
+        case 2: g_tune_force_plain = value; return 0;
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+extern "C" long long bw_launch_count(int reset) {
+    return reset ? g_launches.exchange(0) : g_launches.load();
+}
+
+extern "C" int bw_version(void) { return 100; }

@@ -1,0 +1,169 @@
+/*
+ * blackwell_b200.h -- C ABI of libblackwell_kernels (sm_100a only).
+ *
+ * The decode hot path of the reference engine -- the INT4 block-16 GEMV, its
+ * activation quantizers, the RMSNorm / SwiGLU / residual glue, GQA decode
+ * attention, KV-cache update and greedy sampling -- as hand-written CUDA for
+ * B200.  Every entry point takes plain device pointers and sizes, enqueues its
+ * work on the caller's stream (a cudaStream_t passed as void*; NULL = default
+ * stream), never synchronises, and returns a cudaError_t value as int
+ * (0 = cudaSuccess, 1 = cudaErrorInvalidValue for rejected arguments).
+ *
+ * "replaces" comments give the declaration in the reference's
+ * include/blackwell/kernels.h (C++ `blackwell::kernels::<name>`) and the
+ * definition in its src/kernels tree.  The C++ symbols of that header are also
+ * exported by the library (see blackwell_b200_dropin.hpp), each forwarding to
+ * the function of the same name here.
+ *
+ * Formats.  Weights: u8 [N][K/2], two offset-binary nibbles per byte (value =
+ * nibble - 8, even k in the low nibble), one scale per 16 consecutive k.
+ * INT4 activations use the same nibble format; INT8 activations are i8 [M][K].
+ * Activation scales are f32 [M][K/16].  Outputs are f32 [M][N].
+ */
+#ifndef BLACKWELL_B200_H_
+#define BLACKWELL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ GEMV -- */
+
+/* W4A4 GEMV, fp32 scales.  K % 16 == 0, M >= 1 (any M; the reference stops at 16
+ * and also rejects N % 16 != 0 -- both are accepted here).
+ * replaces gemv_int4_batched: kernels.h:1290-1299, src/kernels/gemv_int8.cu:913-1024 */
+int bw_gemv_int4_batched(float* y_out, const uint8_t* x_packed, const float* x_scale, const uint8_t* W_packed,
+                         const float* W_scale, int K, int N, int M, void* stream);
+
+/* Same arithmetic, one sequence.
+ * replaces gemv_int4_warp: kernels.h:755-763, src/kernels/gemv_int8.cu:481-535,881-900 */
+int bw_gemv_int4_warp(float* y_out, const void* x_packed, const float* x_scale, const void* W_packed,
+                      const float* W_scale, int K, int N, void* stream);
+
+/* W4A8 GEMV: int8 activations (from bw_quantize_int8*), binary16 weight scales
+ * (passed as uint16_t bit patterns).  Extension; arithmetic follows
+ * src/kernels/gemv_int8.cu:937-965 with the int8 operand of :718-748. */
+int bw_gemv_w4a8(float* y_out, const int8_t* x_q, const float* x_scale, const uint8_t* W_packed,
+                 const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
+
+/* W4A8 GEMV with the activation quantizer fused into the prologue: x is
+ * binary16 [M][K].  M <= 8, K % 32 == 0, 16-byte aligned pointers. */
+int bw_gemv_w4a8_f16in(float* y_out, const uint16_t* x_f16, const uint8_t* W_packed, const uint16_t* W_scale_f16,
+                       int K, int N, int M, void* stream);
+
+/* Same with f32 activations and an optional RMSNorm (norm_weight != NULL):
+ * y = W . q8(rmsnorm(x) ) -- fuses fused_rmsnorm (kernels.h:117-133) +
+ * quantize_int8 (kernels.h:526-531) + the GEMV.  M <= 8. */
+int bw_gemv_w4a8_f32in(float* y_out, const float* x_f32, const float* norm_weight, float eps,
+                       const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
+
+/* y = W . q8(silu(gate) * up): fuses apply_swiglu (kernels.h:155-160) +
+ * quantize_int8 + the GEMV (the down projection).  M <= 8. */
+int bw_gemv_w4a8_swiglu(float* y_out, const float* gate, const float* up, const uint8_t* W_packed,
+                        const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
+
+/* Reference-format (W4A4, fp32 scales) GEMV with fused prologues: the int4
+ * quantize rule of quantize_int4 (kernels.h:800-816) applied to x, to
+ * rmsnorm(x) (norm_weight != NULL) or to silu(gate)*up (up != NULL).  M <= 8. */
+int bw_gemv_int4_fused(float* y_out, const float* x_f32, const float* up_or_null, const float* norm_weight_or_null,
+                       float eps, const uint8_t* W_packed, const float* W_scale, int K, int N, int M, void* stream);
+
+/* Debug/inspection: per-block integer dot products of one sequence,
+ * dots i32 [N][K/16], produced by the same unpack + dp4a code as the GEMVs.
+ * x is INT4-packed (a8 == 0) or int8 (a8 != 0). */
+int bw_gemv_block_dots(int32_t* dots, const void* x, int a8, const uint8_t* W_packed, int K, int N, void* stream);
+
+/* ------------------------------------------------------------- quantizers -- */
+
+/* replaces quantize_int4: kernels.h:800-805, src/kernels/gemv_int8.cu:1628-1683 */
+int bw_quantize_int4(void* x_out_packed, float* x_out_sc, const float* in_fp32, int K, void* stream);
+/* replaces quantize_int4_batched: kernels.h:810-816, src/kernels/gemv_int8.cu:1685-1704 */
+int bw_quantize_int4_batched(void* x_out_packed, float* x_out_sc, const float* in_fp32, int K, int M, void* stream);
+/* replaces quantize_int8: kernels.h:526-531, src/kernels/gemv_int8.cu:718-764 */
+int bw_quantize_int8(void* out_int8, float* out_scale, const float* in_fp32, int num_elements, void* stream);
+/* Extension: the same int8 rule on binary16 input. */
+int bw_quantize_int8_f16(void* out_int8, float* out_scale, const uint16_t* in_f16, int num_elements, void* stream);
+/* replaces fused_rmsnorm_quant_int4: kernels.h:417-424, src/kernels/fused_int4_ops.cu:155-242,335-358
+ * (scale rule fmaxf(absmax/7, 1e-9), clamp +-7).  Correct for any N % 32 == 0. */
+int bw_fused_rmsnorm_quant_int4(uint8_t* x_out_packed, float* x_out_scale, const float* proj, const float* weight,
+                                int N, float eps, void* stream);
+/* replaces fused_swiglu_quant_int4: kernels.h:819-825, src/kernels/fused_int4_ops.cu:254-389 */
+int bw_fused_swiglu_quant_int4(uint8_t* out_packed, float* out_scale, const float* gate, const float* up, int N,
+                               void* stream);
+
+/* -------------------------------------------------- norm and elementwise -- */
+
+/* replaces fused_rmsnorm: kernels.h:127-133, src/kernels/norm.cu:44-89,157-165.
+ * All num_elements take part (the reference drops elements >= 4096). */
+int bw_fused_rmsnorm(float* out, const float* inp, const float* weight, int num_elements, float eps, void* stream);
+/* replaces fused_rmsnorm_batched: kernels.h:117-125, src/kernels/norm.cu:114-177 */
+int bw_fused_rmsnorm_batched(float* out, const float* inp, const float* weight, int H, float eps, int M,
+                             void* stream);
+/* replaces apply_swiglu: kernels.h:155-160, src/kernels/norm.cu:94-106,179-189 */
+int bw_apply_swiglu(float* out, const float* gate, const float* up, int num_elements, void* stream);
+/* replaces vector_add_fp32: kernels.h:164-169, src/kernels/norm.cu:191-216 */
+int bw_vector_add_fp32(float* out, const float* a, const float* b, int num_elements, void* stream);
+/* replaces fused_rope_decode: kernels.h:145-153, src/kernels/rope.cu:160-239 */
+int bw_fused_rope_decode(float* out_inplace, const float* cos_cache, const float* sin_cache, const int* seq_pos_ptr,
+                         int heads, int head_dim, int max_seq_len, void* stream);
+
+/* ---------------------------------------------------- KV cache, attention -- */
+
+/* replaces update_kv_cache: kernels.h:309-319, src/kernels/decode.cu:27-46,590-618.
+ * seq_pos is passed by value (no host-to-device copy is enqueued). */
+int bw_update_kv_cache(float* k_cache, float* v_cache, const float* k_new, const float* v_new, int batch_idx,
+                       int seq_pos, int num_heads, int head_dim, int max_seq_len, void* stream);
+/* replaces update_kv_cache_device: kernels.h:322-332, src/kernels/decode.cu:620-639 */
+int bw_update_kv_cache_device(float* k_cache, float* v_cache, const float* k_new, const float* v_new, int batch_idx,
+                              const int* d_seq_pos, int num_heads, int head_dim, int max_seq_len, void* stream);
+/* replaces attention_decode_batched_gqa: kernels.h:202-215, src/kernels/decode.cu:375-512.
+ * head_dim must be 128.  Any seq_pos < max_seq_len (the reference caps the context at 3968). */
+int bw_attention_decode_batched_gqa(float* output, const float* Q, const float* K_cache, const float* V_cache,
+                                    int seq_pos, int num_q_heads, int num_kv_heads, int head_dim, int max_seq_len,
+                                    int M, size_t kv_batch_elems, size_t kv_layer_elems, void* stream);
+/* replaces attention_decode_batched_gqa_device: kernels.h:218-231, src/kernels/decode.cu:514-549 */
+int bw_attention_decode_batched_gqa_device(float* output, const float* Q, const float* K_cache, const float* V_cache,
+                                           const int* d_seq_pos, int num_q_heads, int num_kv_heads, int head_dim,
+                                           int max_seq_len, int M, size_t kv_batch_elems, size_t kv_layer_elems,
+                                           void* stream);
+
+/* Extension: the same attention over a binary16 cache with one position per
+ * sequence (d_seq_pos[M], device memory).  ctx_hint is an upper bound on
+ * seq_pos + 1 used to size the context splits (0 = max_seq_len).  Arithmetic
+ * follows src/kernels/decode.cu:431-465; strides are in cache elements. */
+int bw_attention_decode_f16kv(float* output, const float* Q, const uint16_t* K_cache, const uint16_t* V_cache,
+                              const int* d_seq_pos, int ctx_hint, int num_q_heads, int num_kv_heads, int head_dim,
+                              int max_seq_len, int M, size_t kv_batch_elems, size_t kv_layer_elems, void* stream);
+
+/* ----------------------------------------------------------------- sampling -- */
+
+/* replaces sample_argmax_gpu: kernels.h:1095-1099, src/kernels/sample_gpu.cu:30-60,250-254 */
+int bw_sample_argmax_gpu(const float* logits, int vocab, int* out_id, void* stream);
+/* replaces sample_gpu: kernels.h:1103-1111, src/kernels/sample_gpu.cu:256-330.
+ * temperature < 0.01 = greedy argmax; otherwise temperature/top-k sampling. */
+int bw_sample_gpu(const float* logits, int vocab, float temperature, int top_k, int* out_id,
+                  unsigned long long rng_seed, int step, void* stream);
+/* replaces apply_repetition_penalty: kernels.h:1117-1123, src/kernels/decode.cu:694-731 */
+int bw_apply_repetition_penalty(float* logits, const int* recent, int num_recent, float penalty, int vocab,
+                                void* stream);
+
+/* ------------------------------------------------------------------ service -- */
+
+/* Reads (and clears) the device status word: 0 = ok, 1 = a kernel gave up on a
+ * bounded wait for a bulk copy.  Synchronises the device. */
+int bw_device_status(int* status_out);
+/* Tuning knobs for experiments: key 0 = ring stages (0 = automatic),
+ * key 1 = CTAs per SM cap (0 = automatic), key 2 = force the plain-load kernel. */
+int bw_set_tuning(int key, int value);
+/* Number of kernels launched by this library since the last call with reset != 0. */
+long long bw_launch_count(int reset);
+/* Library version, for load checks. */
+int bw_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BLACKWELL_B200_H_ */
