@@ -114,7 +114,7 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 struct StreamPlan {
     bool ok = false;
-    int Tg = 0, G = 0, J = 0, S = 0, T = 0, row_unit = 1, n_rows = 0, grid = 0;
+    int Tg = 0, G = 0, J = 0, S = 0, T = 0, rg = 0, row_unit = 1, n_rows = 0, grid = 0;
     size_t smem = 0;
 };
 
@@ -200,11 +200,18 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
     p.G = 256 / p.Tg;
     if (p.G < 1) p.G = 1;
     p.T = p.Tg * p.G;
-    const int RG = M <= 2 ? 8 : (M <= 4 ? 4 : 2);
-    const int R = RG * p.G;
+    int rg = M <= 2 ? 8 : (M <= 4 ? 4 : 2);
     const size_t row_nib = (size_t)K / 2, row_sc = (size_t)(K / 16) * ws_bytes;
-    const size_t stage = align128(R * row_nib) + align128(R * row_sc);
     const size_t fixed = GemvSmem::kXOff + align128(gemv_x_smem_bytes(M, nch, p.J));
+    if (fixed >= (size_t)kMaxDynSmem) return p;
+    auto stage_of = [&](int rows_per_group) {
+        const size_t R = (size_t)rows_per_group * p.G;
+        return align128(R * row_nib) + align128(R * row_sc);
+    };
+    // fewer rows per tile when three stages of the full tile do not fit
+    while (rg > 1 && fixed + 3 * stage_of(rg) > (size_t)kMaxDynSmem) rg /= 2;
+    const size_t stage = stage_of(rg);
+    p.rg = rg;
     if (fixed + 2 * stage > (size_t)kMaxDynSmem) return p;
     int S = (int)(((size_t)kMaxDynSmem - fixed) / stage);
     int want = g_tune_stages.load();
@@ -244,7 +251,7 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
         const StreamPlan p = plan_stream(b, mc, (int)sizeof(WS));
         int done = 0;
         if (p.ok) {
-            b.Tg = p.Tg; b.G = p.G; b.J = p.J; b.S = p.S;
+            b.Tg = p.Tg; b.G = p.G; b.J = p.J; b.S = p.S; b.rg = p.rg;
             b.row_unit = p.row_unit; b.n_rows = p.n_rows;
             cudaError_t e = launch_stream<WS>(b, p, mc, st);
             if (e != cudaSuccess) return e;

@@ -62,6 +62,7 @@ struct GemvArgs {
     int nch;                // K / 32
     int Tg, G, J;           // threads covering K, groups, passes over K
     int S;                  // ring stages
+    int rg;                 // rows per group in one tile (<= RowsPerGroup<M>)
 };
 
 // 16 floats (one k-block) -> signed bytes in nibble order + scale/16.
@@ -234,7 +235,7 @@ gemv_w4_stream_kernel(const GemvArgs a) {
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int T = blockDim.x;
     const int K = a.K, nch = a.nch, Tg = a.Tg, G = a.G, S = a.S;
-    const int R = RG * G;
+    const int R = a.rg * G;  // rows per tile; a.rg <= RG
     const int g = t / Tg, tg = t - g * Tg;
     const int warps_per_group = Tg >> 5;
     const uint32_t row_nib = (uint32_t)(K / 2);

@@ -22,8 +22,9 @@ def _edge_activations(M, K, seed):
     x = synth.activations_f16(M, K, seed).astype(np.float32)
     x[0, :16] = 0.0                  # all-zero block
     x[0, 16:32] = 3e-11              # below both degenerate thresholds
-    x[-1, 32:48] = 1000.0            # equal magnitudes: every element hits the clamp
-    x[-1, 48] = -7.5 * (np.abs(x[-1, 48:64]).max() / 7)  # tie cases around .5
+    if K >= 64:
+        x[-1, 32:48] = 1000.0        # equal magnitudes: every element hits the clamp
+        x[-1, 48] = -7.5 * (np.abs(x[-1, 48:64]).max() / 7)  # a value beyond the block's own range
     return x
 
 
