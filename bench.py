@@ -49,8 +49,15 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+_ONLY = None  # (name, N override or None): restricts the set to one matrix, for profiling runs
+
+
 def gemv_set(shape=shapes.QWEN3_8B):
-    return shape.gemv_set()
+    mats = shape.gemv_set()
+    if _ONLY:
+        name, n = _ONLY
+        mats = [(nm, n or N, K) for nm, N, K in mats if nm == name]
+    return mats
 
 
 def set_bytes(mats, M=1, x_kind="f16"):
@@ -103,7 +110,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.02)
+            self._stop.wait(0.005)
 
     def stop(self):
         self._stop.set()
@@ -187,6 +194,10 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     mats = gemv_set()
     M = 1
+    if args.tune:
+        for kv in args.tune.split(","):
+            a, b = kv.split("=")
+            k.set_tuning(int(a), int(b))
     plan = tp.shard_gemv_set(mats, world, rank)
 
     # resident state: this rank's shard of the five matrices, activations, outputs
@@ -212,17 +223,33 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    # One step is captured into a CUDA graph and replayed: the five launches (and the exchanges, for N > 1)
+    # are then issued by the GPU front end back to back, with no per-launch host cost in the timed region.
+    use_graph = not args.no_graph
+    k.launch_count(reset=True)
+    if use_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        launches_per_step = k.launch_count()
+        run_step = graph.replay
+    else:
+        step()
+        launches_per_step = k.launch_count()
+        run_step = step
+    for _ in range(3):
+        run_step()
+    barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    k.launch_count(reset=True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     for _ in range(args.steps):
-        step()
+        run_step()
     e1.record()
     barrier()
-    launches = k.launch_count()
+    launches = launches_per_step * args.steps
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
     if world > 1:
@@ -242,14 +269,25 @@ def run_ours(args, rank, world, local_rank):
     h2d = sum(h.numel() * 2 for h in host_x)
     d2h = sum(h.numel() * 4 for h in host_y)
 
-    def e2e_step():
+    def e2e_enqueue():
         for hx, hy, (sh, W, sc, x, y) in zip(host_x, host_y, state):
             x.copy_(hx, non_blocking=True)
             k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
             if coll is not None:
                 coll.finish(sh, y)
             hy.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller reads the result every step
+
+    if use_graph:
+        e2e_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(e2e_graph):
+            e2e_enqueue()
+        e2e_run = e2e_graph.replay
+    else:
+        e2e_run = e2e_enqueue
+
+    def e2e_step():
+        e2e_run()
+        torch.cuda.current_stream().synchronize()  # the caller reads the result on the host every step
 
     for _ in range(3):
         e2e_step()
@@ -305,7 +343,8 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": "qwen3-8b-shape per-layer GEMV set, M=1, W4A8 block-16 (configs[1])",
                    "matrices": [[n, N, K] for n, N, K in mats], "bytes_per_step": total_bytes,
                    "l2": "inputs larger than L2 (498 MB set, 126 MB L2)",
-                   "parallelism": "tp%d" % world if world > 1 else "single"},
+                   "parallelism": "tp%d" % world if world > 1 else "single",
+                   "launch": "cuda graph replay, one step per graph" if use_graph else "host launches"},
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "clocks": clocks,
@@ -321,10 +360,18 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying "
+                    "a captured CUDA graph")
+    ap.add_argument("--only", default=None, help="profiling aid: run one matrix of the set, NAME or NAME:ROWS")
+    ap.add_argument("--tune", default=None, help="profiling aid: comma list of key=value for bw_set_tuning")
     args = ap.parse_args()
+    global _ONLY
+    if args.only:
+        nm, _, n = args.only.partition(":")
+        _ONLY = (nm, int(n) if n else None)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(128) block_dots_kernel(int32_t* dots, const ui
 // --------------------------------------------------------------------------
 // Host side
 // --------------------------------------------------------------------------
-static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0};
+static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0}, g_tune_rg{0}, g_tune_threads{0};
 static std::atomic<long long> g_launches{0};
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -128,10 +128,24 @@ static cudaError_t launch_stream_inst(const GemvArgs& a, const StreamPlan& p, cu
         attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem);
     });
     if (attr_err != cudaSuccess) return attr_err;
-    int occ = 1;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, p.T, p.smem);
-    if (e != cudaSuccess) return e;
-    if (occ < 1) return cudaErrorInvalidConfiguration;
+    // resident CTAs per SM for this launch shape, remembered per device (a handful of shapes recur)
+    struct OccEntry { int T; size_t smem; int occ; };
+    static OccEntry cache[kMaxDevices][8];
+    static int cache_n[kMaxDevices] = {0};
+    static std::mutex cache_mu;
+    int occ = 0;
+    {
+        std::lock_guard<std::mutex> lk(cache_mu);
+        for (int i = 0; i < cache_n[dev]; ++i)
+            if (cache[dev][i].T == p.T && cache[dev][i].smem == p.smem) occ = cache[dev][i].occ;
+        if (occ == 0) {
+            cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, p.T, p.smem);
+            if (e != cudaSuccess) return e;
+            if (occ < 1) return cudaErrorInvalidConfiguration;
+            cache[dev][cache_n[dev] % 8] = OccEntry{p.T, p.smem, occ};
+            if (cache_n[dev] < 8) ++cache_n[dev];
+        }
+    }
     const int cap = g_tune_ctas.load();
     if (cap > 0 && occ > cap) occ = cap;
     const int units = p.n_rows / p.row_unit;
@@ -197,10 +211,12 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
     const int tmax = M <= 2 ? 512 : 256;
     p.J = (nch + tmax - 1) / tmax;
     p.Tg = (((nch + p.J - 1) / p.J) + 31) / 32 * 32;
-    p.G = 256 / p.Tg;
+    const int tt = g_tune_threads.load() > 0 ? g_tune_threads.load() : 256;
+    p.G = tt / p.Tg;
     if (p.G < 1) p.G = 1;
     p.T = p.Tg * p.G;
     int rg = M <= 2 ? 8 : (M <= 4 ? 4 : 2);
+    if (g_tune_rg.load() > 0 && g_tune_rg.load() < rg) rg = g_tune_rg.load();
     const size_t row_nib = (size_t)K / 2, row_sc = (size_t)(K / 16) * ws_bytes;
     const size_t fixed = GemvSmem::kXOff + align128(gemv_x_smem_bytes(M, nch, p.J));
     if (fixed >= (size_t)kMaxDynSmem) return p;
@@ -216,9 +232,11 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
     int S = (int)(((size_t)kMaxDynSmem - fixed) / stage);
     int want = g_tune_stages.load();
     if (want <= 0) {
-        // keep at least ~64 KB of weights in flight per CTA, leave room for 2 CTAs per SM when cheap
-        want = (int)((65536 + stage - 1) / stage);
-        if (want < 3) want = 3;
+        // Two resident CTAs per SM hide each other's barrier and reduction phases, which measured faster
+        // than one CTA with a deeper ring: take as many stages (up to 4) as half an SM's shared memory holds.
+        const size_t half_sm = (size_t)(228 * 1024 / 2 - 1024 - 512);
+        want = fixed + 2 * stage <= half_sm ? (int)((half_sm - fixed) / stage) : 4;
+        if (want > 4) want = 4;
     }
     if (S > want) S = want;
     if (S > 8) S = 8;
@@ -359,6 +377,8 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 0: g_tune_stages = value; return 0;
         case 1: g_tune_ctas = value; return 0;
         case 2: g_tune_force_plain = value; return 0;
+        case 3: g_tune_rg = value; return 0;
+        case 4: g_tune_threads = value; return 0;
         default: return cudaErrorInvalidValue;
     }
 }

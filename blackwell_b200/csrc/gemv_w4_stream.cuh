@@ -207,6 +207,49 @@ template <> struct ScalePair<float> {
     }
 };
 
+// NR rows of one chunk column, all valid: every weight and scale load is issued
+// before the arithmetic so that the rows overlap in the pipelines.
+template <int M, typename WS, int NR>
+__device__ __forceinline__ void rows_full(const unsigned char* st, size_t stage_nib, uint32_t row_nib,
+                                          uint32_t row_sc, int g, int G, int c, const XChunk (&xr)[M],
+                                          float* acc) {
+    uint4 w[NR];
+    float ws0[NR], ws1[NR];
+#pragma unroll
+    for (int rr = 0; rr < NR; ++rr) {
+        const int r = g + G * rr;
+        w[rr] = *reinterpret_cast<const uint4*>(st + (size_t)r * row_nib + 16 * (size_t)c);
+        ScalePair<WS>::load(st + stage_nib + (size_t)r * row_sc, (size_t)c, ws0[rr], ws1[rr]);
+    }
+#pragma unroll
+    for (int rr = 0; rr < NR; ++rr) chunk_fma<M>(w[rr], ws0[rr], ws1[rr], xr, acc + rr * M);
+}
+
+// One chunk column of a tile for this thread's group: `rg` rows when the tile is
+// full, a predicated walk over the valid rows of a ragged last tile otherwise.
+template <int M, typename WS, int RG>
+__device__ __forceinline__ void tile_column(const unsigned char* st, size_t stage_nib, uint32_t row_nib,
+                                            uint32_t row_sc, int g, int G, int c, int rows, int rg,
+                                            const XChunk (&xr)[M], float* acc) {
+    const bool full = g + G * (rg - 1) < rows;
+    if (full && rg == RG) {
+        rows_full<M, WS, RG>(st, stage_nib, row_nib, row_sc, g, G, c, xr, acc);
+    } else if (full && RG >= 4 && rg == RG / 2) {
+        rows_full<M, WS, (RG >= 2 ? RG / 2 : 1)>(st, stage_nib, row_nib, row_sc, g, G, c, xr, acc);
+    } else {
+#pragma unroll
+        for (int rr = 0; rr < RG; ++rr) {
+            const int r = g + G * rr;
+            if (r < rows) {
+                const uint4 w = *reinterpret_cast<const uint4*>(st + (size_t)r * row_nib + 16 * (size_t)c);
+                float ws0, ws1;
+                ScalePair<WS>::load(st + stage_nib + (size_t)r * row_sc, (size_t)c, ws0, ws1);
+                chunk_fma<M>(w, ws0, ws1, xr, acc + rr * M);
+            }
+        }
+    }
+}
+
 template <int M> struct RowsPerGroup { static constexpr int value = M <= 2 ? 8 : (M <= 4 ? 4 : 2); };
 
 // Shared memory carve-up (byte offsets from the 128-aligned dynamic base).
@@ -220,7 +263,8 @@ struct GemvSmem {
 };
 
 __host__ __device__ inline size_t gemv_x_smem_bytes(int M, int nch, int J) {
-    return J > 1 ? (size_t)M * nch * 40 : 0;
+    (void)J;
+    return (size_t)M * nch * 40;
 }
 __host__ __device__ inline size_t align128(size_t v) { return (v + 127) & ~(size_t)127; }
 
@@ -306,34 +350,39 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         __syncthreads();
     }
 
-    XChunk xr[M];
-    if (!kMultiPass) {
-        if (tg < nch) {
-#pragma unroll
-            for (int m = 0; m < M; ++m) make_xchunk(a, m, tg, needs_norm ? rstd_s[m] : 1.f, xr[m]);
-        } else {
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) { xr[m].e[i] = 0; xr[m].o[i] = 0; }
-                xr[m].s[0] = xr[m].s[1] = 0.f;
-            }
-        }
-    } else {
-        // stage every chunk of every sequence in shared memory: [m][c] x {uint4 e, uint4 o, float2 s}
-        uint4* xe = reinterpret_cast<uint4*>(xs_base);
-        uint4* xo = xe + (size_t)M * nch;
-        float2* xsv = reinterpret_cast<float2*>(xo + (size_t)M * nch);
-        for (int idx = t; idx < M * nch; idx += T) {
-            const int m = idx / nch, c = idx - m * nch;
-            XChunk xc;
-            make_xchunk(a, m, c, needs_norm ? rstd_s[m] : 1.f, xc);
-            xe[idx] = make_uint4(xc.e[0], xc.e[1], xc.e[2], xc.e[3]);
-            xo[idx] = make_uint4(xc.o[0], xc.o[1], xc.o[2], xc.o[3]);
-            xsv[idx] = make_float2(xc.s[0], xc.s[1]);
+    // Every k-block of every sequence is produced exactly once per CTA and staged in shared memory in
+    // chunk order: [m][c] x {uint4 even-k words, uint4 odd-k words, float2 scales}.
+    {
+        uint2* xe2 = reinterpret_cast<uint2*>(xs_base);
+        uint2* xo2 = xe2 + (size_t)M * nch * 2;
+        float* xs1 = reinterpret_cast<float*>(xo2 + (size_t)M * nch * 2);
+        const int nkb = 2 * nch;
+        for (int idx = t; idx < M * nkb; idx += T) {
+            const int m = idx / nkb, kb = idx - m * nkb;
+            uint32_t e[2], o[2];
+            float sc;
+            make_xblock(a, m, kb, needs_norm ? rstd_s[m] : 1.f, e, o, sc);
+            xe2[idx] = make_uint2(e[0], e[1]);
+            xo2[idx] = make_uint2(o[0], o[1]);
+            xs1[idx] = sc;
         }
         __syncthreads();
     }
+    const uint4* xe = reinterpret_cast<const uint4*>(xs_base);
+    const uint4* xo = xe + (size_t)M * nch;
+    const float2* xsv = reinterpret_cast<const float2*>(xo + (size_t)M * nch);
+    XChunk xr[M];
+    auto load_x = [&](int c) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const uint4 e = xe[m * nch + c], o = xo[m * nch + c];
+            const float2 sv = xsv[m * nch + c];
+            xr[m].e[0] = e.x; xr[m].e[1] = e.y; xr[m].e[2] = e.z; xr[m].e[3] = e.w;
+            xr[m].o[0] = o.x; xr[m].o[1] = o.y; xr[m].o[2] = o.z; xr[m].o[3] = o.w;
+            xr[m].s[0] = sv.x; xr[m].s[1] = sv.y;
+        }
+    };
+    if (!kMultiPass && tg < nch) load_x(tg);
 
     // ------------------------------------------------------------- main loop
     bool aborted = false;
@@ -351,43 +400,13 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         for (int i = 0; i < V; ++i) acc[i] = 0.f;
 
         if (!kMultiPass) {
-            if (tg < nch) {
-#pragma unroll
-                for (int rr = 0; rr < RG; ++rr) {
-                    const int r = g + G * rr;
-                    if (r < rows) {
-                        const uint4 w = *reinterpret_cast<const uint4*>(st + (size_t)r * row_nib + 16 * (size_t)tg);
-                        float ws0, ws1;
-                        ScalePair<WS>::load(st + stage_nib + (size_t)r * row_sc, (size_t)tg, ws0, ws1);
-                        chunk_fma<M>(w, ws0, ws1, xr, &acc[rr * M]);
-                    }
-                }
-            }
+            if (tg < nch) tile_column<M, WS, RG>(st, stage_nib, row_nib, row_sc, g, G, tg, rows, a.rg, xr, acc);
         } else {
-            const uint4* xe = reinterpret_cast<const uint4*>(xs_base);
-            const uint4* xo = xe + (size_t)M * nch;
-            const float2* xsv = reinterpret_cast<const float2*>(xo + (size_t)M * nch);
             for (int j = 0; j < a.J; ++j) {
                 const int c = tg + Tg * j;
                 if (c < nch) {
-#pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        const uint4 e = xe[m * nch + c], o = xo[m * nch + c];
-                        const float2 sv = xsv[m * nch + c];
-                        xr[m].e[0] = e.x; xr[m].e[1] = e.y; xr[m].e[2] = e.z; xr[m].e[3] = e.w;
-                        xr[m].o[0] = o.x; xr[m].o[1] = o.y; xr[m].o[2] = o.z; xr[m].o[3] = o.w;
-                        xr[m].s[0] = sv.x; xr[m].s[1] = sv.y;
-                    }
-#pragma unroll
-                    for (int rr = 0; rr < RG; ++rr) {
-                        const int r = g + G * rr;
-                        if (r < rows) {
-                            const uint4 w = *reinterpret_cast<const uint4*>(st + (size_t)r * row_nib + 16 * (size_t)c);
-                            float ws0, ws1;
-                            ScalePair<WS>::load(st + stage_nib + (size_t)r * row_sc, (size_t)c, ws0, ws1);
-                            chunk_fma<M>(w, ws0, ws1, xr, &acc[rr * M]);
-                        }
-                    }
+                    load_x(c);
+                    tile_column<M, WS, RG>(st, stage_nib, row_nib, row_sc, g, G, c, rows, a.rg, xr, acc);
                 }
             }
         }
