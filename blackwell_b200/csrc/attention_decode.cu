@@ -13,6 +13,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <float.h>
+#include <stdio.h>
 
 #include <mutex>
 
@@ -299,6 +300,98 @@ extern "C" int bw_attention_decode_f16kv(float* output, const float* Q, const ui
     a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
     a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
     return attn_launch<__half>(a, ctx_hint > 0 ? ctx_hint : max_seq_len, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------
+// Attention without any allocation.
+//
+// Some hosts of this library must never reach the CUDA allocator once they are
+// running: a server that has handed the whole GPU to its own pool, a process
+// that runs with allocation disabled after start-up, a caller whose memory
+// budget is audited to the byte.  For them the split partials live in a
+// fixed array that is part of the library image instead of a cudaMalloc'd
+// buffer.  Every GPU that loads the library carries these 2 MiB until exit.
+// ---------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchFloats = (size_t)1 << 19;  // 2 MiB of split partials at most
+static __device__ __align__(256) float g_attn_noalloc_scratch[kNoAllocScratchFloats];
+// Device address of the array, per device.  In host code the array's name stands for a host-side shadow of the
+// symbol, not for device memory, so the address a kernel can use has to be asked for with the device current.
+static float* g_attn_noalloc_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_attn_noalloc_mu;
+
+static cudaError_t attn_noalloc_scratch(float** out) {
+    std::lock_guard<std::mutex> lk(g_attn_noalloc_mu);
+    const int dev = current_device();
+    if (!g_attn_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        g_attn_noalloc_ptr[dev] = p;
+    }
+    *out = g_attn_noalloc_ptr[dev];
+    return cudaSuccess;
+}
+
+// Same arithmetic, same context splitting and same kernels as bw_attention_decode_batched_gqa_device, with the
+// partial records in the fixed array.  No partial has to start from zero: every (head, split) record that the
+// merge kernel reads is written in full by the split kernel of the same call, empty splits included.
+extern "C" int bw_attention_decode_batched_gqa_noalloc(float* output, const float* Q, const float* K_cache,
+                                                       const float* V_cache, const int* d_seq_pos, int num_q_heads,
+                                                       int num_kv_heads, int head_dim, int max_seq_len, int M,
+                                                       size_t kv_batch_elems, size_t kv_layer_elems, void* stream) {
+    if (head_dim != kHd || !d_seq_pos) return cudaErrorInvalidValue;
+    if (!output || !Q || !K_cache || !V_cache || num_q_heads < 1 || num_kv_heads < 1 ||
+        num_q_heads % num_kv_heads != 0 || M < 1 || max_seq_len < 1)
+        return cudaErrorInvalidValue;
+    const int gq = num_q_heads / num_kv_heads;
+    if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return cudaErrorInvalidValue;
+    AttnArgs a{};
+    a.out = output; a.Q = Q; a.K = K_cache; a.V = V_cache; a.d_seq_pos = d_seq_pos; a.per_seq = 0;
+    a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
+    a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
+    // the split rule of attn_launch, with the whole cache as the context bound
+    const int ctx = max_seq_len;
+    const int sms = sm_count(current_device());
+    int nsplit = (2 * sms + M * a.nkv - 1) / (M * a.nkv);
+    const int max_split = (ctx + 63) / 64;
+    if (nsplit > max_split) nsplit = max_split;
+    if (nsplit > 64) nsplit = 64;
+    if (nsplit < 1) nsplit = 1;
+    a.split_len = (ctx + nsplit - 1) / nsplit;
+    a.split_len = (a.split_len + kPosPerStep - 1) / kPosPerStep * kPosPerStep;
+    nsplit = (ctx + a.split_len - 1) / a.split_len;
+    a.nsplit = nsplit;
+    a.scale = 1.0f / sqrtf((float)kHd);
+    a.part = nullptr;
+    const size_t need = (size_t)M * a.nqh * nsplit * kPartStride;
+    if (nsplit > 1) {
+        if (need > kNoAllocScratchFloats) {
+            fprintf(stderr,
+                    "bw_attention_decode_batched_gqa_noalloc: M * num_q_heads * splits * %d = %zu floats of split "
+                    "partials exceed the fixed scratch of %zu floats; use the allocating entry point or a smaller "
+                    "batch\n", kPartStride, need, kNoAllocScratchFloats);
+            return cudaErrorInvalidValue;
+        }
+        cudaError_t e = attn_noalloc_scratch(&a.part);
+        if (e != cudaSuccess) return e;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const dim3 grid(nsplit, a.nkv, a.M);
+    switch (gq) {
+        case 1: attn_decode_split_kernel<float, 1><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+        case 2: attn_decode_split_kernel<float, 2><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+        case 4: attn_decode_split_kernel<float, 4><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+        default: attn_decode_split_kernel<float, 8><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+    }
+    count_launch(1);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return e;
+    if (nsplit > 1) {
+        attn_merge_kernel<<<a.M * a.nqh, kHd, 0, st>>>(a.out, a.part, nsplit);
+        count_launch(1);
+        e = cudaPeekAtLastError();
+    }
+    return e;
 }
 
 static int update_kv_impl(float* k_cache, float* v_cache, const float* k_new, const float* v_new, int batch_idx,

@@ -203,3 +203,12 @@ def set_tuning(key: int, value: int) -> None:
 
 def launch_count(reset: bool = False) -> int:
     return int(_L.bw_launch_count(1 if reset else 0))
+
+
+def attention_decode_batched_gqa_noalloc(output, Q, K_cache, V_cache, d_seq_pos, num_q_heads, num_kv_heads,
+                                         head_dim, max_seq_len, M, kv_batch_elems, kv_layer_elems, stream=None):
+    """Attention for callers that must not allocate (no counterpart in the reference): same arguments and
+    results as ``attention_decode_batched_gqa_device``, split partials in a fixed 2 MiB array of the library."""
+    _chk("attention_decode_batched_gqa_noalloc", _L.bw_attention_decode_batched_gqa_noalloc(
+        _p(output), _p(Q), _p(K_cache), _p(V_cache), _p(d_seq_pos), num_q_heads, num_kv_heads, head_dim,
+        max_seq_len, M, C.c_size_t(kv_batch_elems), C.c_size_t(kv_layer_elems), _s(stream)))

@@ -138,6 +138,28 @@ int bw_attention_decode_f16kv(float* output, const float* Q, const uint16_t* K_c
                               const int* d_seq_pos, int ctx_hint, int num_q_heads, int num_kv_heads, int head_dim,
                               int max_seq_len, int M, size_t kv_batch_elems, size_t kv_layer_elems, void* stream);
 
+/* Attention for callers that must not allocate.  No counterpart in the reference: it exists for hosts
+ * that cannot reach the CUDA allocator once they are serving -- a process that has given all device memory
+ * to its own pool, or one that runs with allocation switched off or audited after start-up.  Arguments,
+ * arithmetic and results are those of bw_attention_decode_batched_gqa_device; the per-split partial results
+ * live in a fixed 2 MiB array inside the library image (every GPU that loads the library carries it until
+ * exit) instead of a buffer obtained from cudaMalloc, and the call makes no cudaMalloc, cudaFree or other
+ * allocating call.
+ *   Limit: M * num_q_heads * splits * 130 floats must fit in 524,288 floats, where splits =
+ *   min(64, ceil(max_seq_len / 64), ceil(2 * SMs / (M * num_kv_heads))) re-derived after rounding the split
+ *   length up to a multiple of 4; larger problems are rejected with cudaErrorInvalidValue and a message on
+ *   stderr.  On a 148-SM B200 every 32-query-head / 8-kv-head shape fits; with 64 query heads over
+ *   8 kv heads, batches of 32 to 36 sequences at long context do not.
+ *   The first call on each device looks up the device address of the array (cudaGetSymbolAddress, with that
+ *   device current); make that first call outside any stream capture.
+ *   All calls share the array and it keeps the previous call's contents (none of it needs clearing: every
+ *   record read is written earlier in the same call).  Two calls whose kernels overlap on one GPU -- different
+ *   streams -- race on it; keep them on one stream or order them. */
+int bw_attention_decode_batched_gqa_noalloc(float* output, const float* Q, const float* K_cache,
+                                            const float* V_cache, const int* d_seq_pos, int num_q_heads,
+                                            int num_kv_heads, int head_dim, int max_seq_len, int M,
+                                            size_t kv_batch_elems, size_t kv_layer_elems, void* stream);
+
 /* ----------------------------------------------------------------- sampling -- */
 
 /* replaces sample_argmax_gpu: kernels.h:1095-1099, src/kernels/sample_gpu.cu:30-60,250-254 */
