@@ -37,7 +37,7 @@ UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the ncu capture
 # summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_RATIO = 1.023  # (dram read + write) / algorithmic bytes of one launch, profiles/gemv_w4_stream_m1_lmhead65536x4096.md
 
 
 def measured_peak():
@@ -349,7 +349,7 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind,
+                     "traffic": int(per_launch_bytes * NCU_TRAFFIC_RATIO), "traffic_note": "ncu capture of a 65536-row slice, scaled by rows", "peak_kind": peak_kind,
                      "kernel": "gemv_w4_stream_kernel<1,half>", "nominal_frac": achieved / 8000.0},
         "cpu_baseline": cpu,
         "per_matrix": per,
