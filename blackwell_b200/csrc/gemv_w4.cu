@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(128) gemv_w4_rows_kernel(const GemvArgs a, int
     if (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4) {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            const float* xr = static_cast<const float*>(a.x) + (size_t)m * K;
+            const float* xr = static_cast<const float*>(a.x) + (size_t)m * a.x_stride;
             float ss = 0.f;
             for (int i = lane; i < K; i += 32) ss = fmaf(xr[i], xr[i], ss);
             ss = warp_sum(ss);
@@ -66,7 +66,10 @@ __global__ void __launch_bounds__(128) gemv_w4_rows_kernel(const GemvArgs a, int
 #pragma unroll
     for (int m = 0; m < M; ++m) {
         const float tot = warp_sum(acc[m]);
-        if (lane == 0) a.y[(size_t)m * a.N + row] = tot;
+        if (lane == 0) {
+            const size_t yi = (size_t)m * a.y_stride + row;
+            a.y[yi] = a.residual ? tot + a.residual[yi] : tot;
+        }
     }
 }
 
@@ -258,11 +261,15 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
     const bool prequant = (a.xkind == kXInt8 || a.xkind == kXInt4);
     if (!prequant && (M > 8 || !aligned(a.x, 16))) return cudaErrorInvalidValue;
     a.nch = a.K / 32;
+    if (a.x_stride <= 0) a.x_stride = a.K;
+    if (a.y_stride <= 0) a.y_stride = a.N;
+    if (a.x_stride % 4 != 0 || a.y_stride < a.N) return cudaErrorInvalidValue;
     // M > 8: passes of up to 8 sequences (pre-quantized operands only).
     for (int m0 = 0; m0 < M; m0 += 8) {
         const int mc = (M - m0) < 8 ? (M - m0) : 8;
         GemvArgs b = a;
-        b.y = a.y + (size_t)m0 * a.N;
+        b.y = a.y + (size_t)m0 * a.y_stride;
+        if (a.residual) b.residual = a.residual + (size_t)m0 * a.y_stride;
         if (a.xkind == kXInt8) b.x = static_cast<const int8_t*>(a.x) + (size_t)m0 * a.K;
         if (a.xkind == kXInt4) b.x = static_cast<const uint8_t*>(a.x) + (size_t)m0 * (a.K / 2);
         if (a.xsc) b.xsc = a.xsc + (size_t)m0 * (a.K / 16);
@@ -336,6 +343,20 @@ extern "C" int bw_gemv_w4a8_swiglu(float* y_out, const float* gate, const float*
     GemvArgs a{};
     a.y = y_out; a.W = W_packed; a.Wsc = W_scale_f16; a.x = gate; a.x2 = up;
     a.xkind = kXSwiglu; a.K = K; a.N = N;
+    return gemv_dispatch<__half>(a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_gemv_w4a8_decode(float* y_out, long y_stride, const float* residual_or_null, const float* x_f32,
+                                   const float* up_or_null, long x_stride, const float* norm_weight_or_null,
+                                   float eps, const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N,
+                                   int M, void* stream) {
+    if (up_or_null && norm_weight_or_null) return cudaErrorInvalidValue;
+    GemvArgs a{};
+    a.y = y_out; a.y_stride = y_stride; a.residual = residual_or_null;
+    a.W = W_packed; a.Wsc = W_scale_f16; a.x = x_f32; a.x2 = up_or_null; a.x_stride = x_stride;
+    a.norm_w = norm_weight_or_null; a.eps = eps;
+    a.xkind = up_or_null ? kXSwiglu : (norm_weight_or_null ? kXFloatNorm : kXFloat);
+    a.K = K; a.N = N;
     return gemv_dispatch<__half>(a, M, static_cast<cudaStream_t>(stream));
 }
 

@@ -54,6 +54,9 @@ struct GemvArgs {
     const void* x2;         // up-projection for kXSwiglu
     const float* xsc;       // [M][K/16] for the pre-quantized kinds
     const float* norm_w;    // [K] for kXFloatNorm
+    const float* residual;  // optional [M][y_stride]: added to the result (may alias y)
+    long x_stride;          // elements between sequences of x / x2 (f16 and f32 kinds)
+    long y_stride;          // elements between sequences of y and residual
     float eps;
     int xkind;
     int K, N;               // N = row count of y; rows >= n_rows are not touched
@@ -109,7 +112,7 @@ __device__ __forceinline__ void make_xblock(const GemvArgs& a, int m, int kb, fl
     } else {
         float v[16];
         if (a.xkind == kXHalf) {
-            const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __half*>(a.x) + (size_t)m * K + 16 * (size_t)kb);
+            const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __half*>(a.x) + (size_t)m * a.x_stride + 16 * (size_t)kb);
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const uint4 q = __ldg(p + i);
@@ -122,7 +125,7 @@ __device__ __forceinline__ void make_xblock(const GemvArgs& a, int m, int kb, fl
                 }
             }
         } else {
-            const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * K + 16 * (size_t)kb);
+            const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * a.x_stride + 16 * (size_t)kb);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float4 f = __ldg(p + i);
@@ -139,7 +142,7 @@ __device__ __forceinline__ void make_xblock(const GemvArgs& a, int m, int kb, fl
                     v[4 * i + 3] = v[4 * i + 3] * gw.w * rstd;
                 }
             } else if (a.xkind == kXSwiglu || a.xkind == kXSwigluI4) {
-                const float4* up = reinterpret_cast<const float4*>(static_cast<const float*>(a.x2) + (size_t)m * K + 16 * (size_t)kb);
+                const float4* up = reinterpret_cast<const float4*>(static_cast<const float*>(a.x2) + (size_t)m * a.x_stride + 16 * (size_t)kb);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float4 u = __ldg(up + i);
@@ -333,7 +336,7 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         // sum of squares of every sequence, all threads cooperating
         for (int m = 0; m < M; ++m) {
             float ss = 0.f;
-            const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * K);
+            const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * a.x_stride);
             for (int i = t; i < K / 4; i += T) {
                 const float4 f = __ldg(p + i);
                 ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); ss = fmaf(f.z, f.z, ss); ss = fmaf(f.w, f.w, ss);
@@ -430,7 +433,8 @@ gemv_w4_stream_kernel(const GemvArgs a) {
                 const int gg = r % G, rr = r / G;
                 float sum = 0.f;
                 for (int w = 0; w < warps_per_group; ++w) sum += redb[(gg * warps_per_group + w) * 32 + rr * M + m];
-                a.y[(size_t)m * a.N + r0 + r] = sum;
+                const size_t yi = (size_t)m * a.y_stride + r0 + r;
+                a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
             }
         }
     }

@@ -212,3 +212,28 @@ def attention_decode_batched_gqa_noalloc(output, Q, K_cache, V_cache, d_seq_pos,
     _chk("attention_decode_batched_gqa_noalloc", _L.bw_attention_decode_batched_gqa_noalloc(
         _p(output), _p(Q), _p(K_cache), _p(V_cache), _p(d_seq_pos), num_q_heads, num_kv_heads, head_dim,
         max_seq_len, M, C.c_size_t(kv_batch_elems), C.c_size_t(kv_layer_elems), _s(stream)))
+
+
+# ------------------------------------------------------------ decode-step glue
+def gemv_w4a8_decode(y_out, y_stride, residual, x_f32, up, x_stride, norm_weight, eps, W_packed, W_scale_f16, K, N,
+                     M, stream=None):
+    _chk("gemv_w4a8_decode", _L.bw_gemv_w4a8_decode(
+        _p(y_out), C.c_long(y_stride), _p(residual), _p(x_f32), _p(up), C.c_long(x_stride), _p(norm_weight),
+        C.c_float(eps), _p(W_packed), _p(W_scale_f16), K, N, M, _s(stream)))
+
+
+def qk_norm_rope_kv_f16(q_out, k_cache, v_cache, qkv, q_norm_w, k_norm_w, d_seq_pos, num_q_heads, num_kv_heads,
+                        head_dim, max_seq_len, M, kv_batch_elems, kv_layer_elems, eps, rope_base, stream=None):
+    _chk("qk_norm_rope_kv_f16", _L.bw_qk_norm_rope_kv_f16(
+        _p(q_out), _p(k_cache), _p(v_cache), _p(qkv), _p(q_norm_w), _p(k_norm_w), _p(d_seq_pos), num_q_heads,
+        num_kv_heads, head_dim, max_seq_len, M, C.c_size_t(kv_batch_elems), C.c_size_t(kv_layer_elems),
+        C.c_float(eps), C.c_float(rope_base), _s(stream)))
+
+
+def embed_gather_f16(x_out, table_f16, d_tokens, H, vocab, M, stream=None):
+    _chk("embed_gather_f16", _L.bw_embed_gather_f16(_p(x_out), _p(table_f16), _p(d_tokens), H, vocab, M, _s(stream)))
+
+
+def sample_argmax_batched(logits, row_stride, vocab, M, out_ids, seq_pos_to_advance=None, stream=None):
+    _chk("sample_argmax_batched", _L.bw_sample_argmax_batched(_p(logits), C.c_long(row_stride), vocab, M,
+                                                              _p(out_ids), _p(seq_pos_to_advance), _s(stream)))

@@ -65,6 +65,16 @@ int bw_gemv_w4a8_f32in(float* y_out, const float* x_f32, const float* norm_weigh
 int bw_gemv_w4a8_swiglu(float* y_out, const float* gate, const float* up, const uint8_t* W_packed,
                         const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
 
+/* The W4A8 GEMV as the decode step uses it: f32 activations with a row stride (x_stride elements between
+ * sequences; 0 = K), one of three fused prologues -- plain quantize, RMSNorm + quantize (norm_weight != NULL),
+ * or SwiGLU + quantize (up != NULL, same stride as x) -- and an optional residual added to the result
+ * (residual may alias y_out; both use y_stride, 0 = N).  It replaces, in one launch, the reference's
+ * fused_rmsnorm / apply_swiglu + quantize + gemv + vector_add_fp32 sequences
+ * (server/inference_server_int4_batched.cu:256-279).  M <= 8. */
+int bw_gemv_w4a8_decode(float* y_out, long y_stride, const float* residual_or_null, const float* x_f32,
+                        const float* up_or_null, long x_stride, const float* norm_weight_or_null, float eps,
+                        const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
+
 /* Reference-format (W4A4, fp32 scales) GEMV with fused prologues: the int4
  * quantize rule of quantize_int4 (kernels.h:800-816) applied to x, to
  * rmsnorm(x) (norm_weight != NULL) or to silu(gate)*up (up != NULL).  M <= 8. */
@@ -137,6 +147,26 @@ int bw_attention_decode_batched_gqa_device(float* output, const float* Q, const 
 int bw_attention_decode_f16kv(float* output, const float* Q, const uint16_t* K_cache, const uint16_t* V_cache,
                               const int* d_seq_pos, int ctx_hint, int num_q_heads, int num_kv_heads, int head_dim,
                               int max_seq_len, int M, size_t kv_batch_elems, size_t kv_layer_elems, void* stream);
+
+/* Batched decode glue, one launch for all M sequences with per-sequence positions in device memory.
+ * Input: the fused QKV projection output qkv f32 [M][(nq + 2 nkv) * 128].  Query and key heads get the per-head
+ * RMSNorm and the interleaved-pair RoPE (theta = pos * rope_base^(-2i/128)) of the reference's caller-side
+ * kernels (server/inference_server_int4_batched.cu:49-70); queries go to q_out f32 [M][nq * 128]; keys and
+ * values are written as binary16 into the cache rows at each sequence's position (the scatter of
+ * update_kv_cache, src/kernels/decode.cu:27-46), cache addressed as in bw_attention_decode_f16kv. */
+int bw_qk_norm_rope_kv_f16(float* q_out, uint16_t* k_cache, uint16_t* v_cache, const float* qkv,
+                           const float* q_norm_w, const float* k_norm_w, const int* d_seq_pos, int num_q_heads,
+                           int num_kv_heads, int head_dim, int max_seq_len, int M, size_t kv_batch_elems,
+                           size_t kv_layer_elems, float eps, float rope_base, void* stream);
+/* x_out f32 [M][H] = table_f16[d_tokens[m]][:] -- the embedding lookup the reference does with a host-side
+ * copy (server/inference_server_int4_batched.cu:251), token ids read from device memory.  H % 8 == 0. */
+int bw_embed_gather_f16(float* x_out, const uint16_t* table_f16, const int* d_tokens, int H, int vocab, int M,
+                        void* stream);
+/* Greedy argmax of each row of logits f32 [M][row_stride] (rule of sample_argmax_gpu,
+ * src/kernels/sample_gpu.cu:30-60) into out_ids[M]; when seq_pos_to_advance is not NULL each of its M entries
+ * is incremented, which closes a decode step inside a CUDA graph.  M <= 256. */
+int bw_sample_argmax_batched(const float* logits, long row_stride, int vocab, int M, int* out_ids,
+                             int* seq_pos_to_advance_or_null, void* stream);
 
 /* Attention for callers that must not allocate.  No counterpart in the reference: it exists for hosts
  * that cannot reach the CUDA allocator once they are serving -- a process that has given all device memory

@@ -1,0 +1,182 @@
+"""One synthetic decode step of a small Qwen3-shaped model through the C ABI against the same chain of oracle
+routines on the CPU (the reference's per-layer sequence, server/inference_server_int4_batched.cu:253-298, with
+int8 activations and a binary16 cache).  Also the glue kernels on their own."""
+import numpy as np
+import pytest
+
+import oracle
+from blackwell_b200 import synth
+from blackwell_b200.shapes import ModelShape
+from tests.util import max_abs_rel, to_dev
+
+pytestmark = pytest.mark.gpu
+
+SMALL = ModelShape("small", layers=2, hidden=256, inter=416, n_q_heads=4, n_kv_heads=2, head_dim=128, vocab=1003)
+
+
+class HostWeights:
+    def __init__(self):
+        self.np = {}
+
+    def __call__(self, N, K, sd):
+        if N == "embed":
+            V, H = K, sd
+            e = synth.activations_f16(V, H, 4242)
+            self.np["embed"] = e
+            return to_dev(e.view(np.uint16)).view(__import__("torch").float16)
+        W, sc16, _ = synth.int4_weights(N, K, sd)
+        self.np[sd] = (W, sc16)
+        return to_dev(W), to_dev(sc16.view(np.uint16)).view(__import__("torch").float16)
+
+
+def cpu_gemv(x, W, sc16):
+    q, s = oracle.quantize_int8(np.ascontiguousarray(x, np.float32))
+    return oracle.gemv_w4a8_f64(q, s, W, sc16).astype(np.float32)
+
+
+def test_decode_step_matches_cpu_chain(cuda):
+    import torch
+
+    from blackwell_b200.decode import ROPE_BASE, DecodeEngine
+
+    s, M, max_seq, ctx = SMALL, 3, 96, 40
+    hw = HostWeights()
+    eng = DecodeEngine(s, M, max_seq, cuda, seed=5, host_weights=hw)
+    eng.fill_cache(ctx)
+    pos0 = np.array([ctx - 1, ctx - 5, 3], np.int32)
+    eng.pos.copy_(torch.from_numpy(pos0))
+    toks = np.array([7, 1002, 500], np.int32)
+    eng.set_tokens(toks)
+    Kc = eng.kc.cpu().numpy().copy()
+    Vc = eng.vc.cpu().numpy().copy()
+    eng.step()
+    torch.cuda.synchronize()
+
+    # ---- CPU chain
+    nq, nkv, H, I = s.n_q_heads, s.n_kv_heads, s.hidden, s.inter
+    x = hw.np["embed"][toks].astype(np.float32)
+    Kc = Kc.reshape(M, s.layers, nkv, max_seq, 128)
+    Vc = Vc.reshape(M, s.layers, nkv, max_seq, 128)
+    for l, L in enumerate(eng.layers):
+        sd = 5 + 1000 * l
+        qkv = cpu_gemv(oracle.rmsnorm(x, L["rn_in"].cpu().numpy()), *hw.np[sd + 1])
+        q = np.empty((M, nq * 128), np.float32)
+        for m in range(M):
+            qm = oracle.rope(oracle.head_norm(qkv[m, :nq * 128], L["qn"].cpu().numpy(), nq, 128), nq, 128, int(pos0[m]))
+            km = oracle.rope(oracle.head_norm(qkv[m, nq * 128:(nq + nkv) * 128], L["kn"].cpu().numpy(), nkv, 128),
+                             nkv, 128, int(pos0[m]))
+            q[m] = qm
+            Kc[m, l, :, pos0[m]] = km.reshape(nkv, 128).astype(np.float16)
+            Vc[m, l, :, pos0[m]] = qkv[m, (nq + nkv) * 128:].reshape(nkv, 128).astype(np.float16)
+        attn = oracle.attention_decode_f16kv(q, np.ascontiguousarray(Kc[:, l]), np.ascontiguousarray(Vc[:, l]), pos0,
+                                             nq, nkv, 128, max_seq, M)
+        x = x + cpu_gemv(attn, *hw.np[sd + 2])
+        gu = cpu_gemv(oracle.rmsnorm(x, L["rn_post"].cpu().numpy()), *hw.np[sd + 3])
+        act = oracle.swiglu(np.ascontiguousarray(gu[:, :I]), np.ascontiguousarray(gu[:, I:]))
+        x = x + cpu_gemv(act, *hw.np[sd + 4])
+    logits = cpu_gemv(oracle.rmsnorm(x, eng.rn_final.cpu().numpy()), *hw.np[5 + 900001])
+
+    assert max_abs_rel(eng.x.cpu().numpy(), x) < 2e-3
+    assert max_abs_rel(eng.logits.cpu().numpy(), logits) < 2e-3
+    got_k = eng.kc.cpu().numpy().reshape(M, s.layers, nkv, max_seq, 128).astype(np.float32)
+    assert max_abs_rel(got_k, Kc.astype(np.float32)) < 2e-3
+    # greedy ids: equal wherever the CPU's top-2 margin exceeds the numerical noise
+    ids = eng.tokens.cpu().numpy()
+    for m in range(M):
+        top = np.sort(logits[m])[-2:]
+        if top[1] - top[0] > 1e-2 * np.abs(logits[m]).max():
+            assert ids[m] == int(np.argmax(logits[m]))
+    assert np.array_equal(eng.pos.cpu().numpy(), pos0 + 1)
+
+
+def test_decode_step_graph_replay_is_deterministic(cuda):
+    import torch
+
+    from blackwell_b200.decode import DecodeEngine
+
+    eng = DecodeEngine(SMALL, 2, 64, cuda, seed=9)
+    eng.fill_cache(20)
+    eng.set_tokens([5, 6])
+    eng.step()  # warm-up outside capture (first-use allocations)
+    torch.cuda.synchronize()
+
+    def run():
+        eng.pos.fill_(19)
+        eng.set_tokens([5, 6])
+        g.replay()
+        g.replay()
+        torch.cuda.synchronize()
+        return eng.tokens.cpu().numpy().copy(), eng.logits.cpu().numpy().copy()
+
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        eng.step()
+    t1, l1 = run()
+    t2, l2 = run()
+    assert np.array_equal(t1, t2) and np.array_equal(l1, l2)
+    assert np.array_equal(eng.pos.cpu().numpy(), [21, 21])
+
+
+def test_qk_norm_rope_kv_and_embed_and_batched_argmax(cuda):
+    import torch
+
+    from blackwell_b200 import kernels as k
+
+    M, nq, nkv, max_seq = 3, 8, 2, 50
+    g = synth.rng(400)
+    qkv = g.normal(size=(M, (nq + 2 * nkv) * 128)).astype(np.float32)
+    qn, kn = synth.norm_weight(128, 401), synth.norm_weight(128, 402)
+    pos = np.array([0, 17, 49], np.int32)
+    layers, layer = 2, 1
+    kv_layer = nkv * max_seq * 128
+    kc = torch.zeros((M, layers * kv_layer), dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    q = torch.empty((M, nq * 128), dtype=torch.float32, device="cuda")
+    k.qk_norm_rope_kv_f16(q, kc, vc, to_dev(qkv), to_dev(qn), to_dev(kn), to_dev(pos), nq, nkv, 128, max_seq, M,
+                          layers * kv_layer, layer * kv_layer, 1e-6, 1e6)
+    kc_n = kc.cpu().numpy().reshape(M, layers, nkv, max_seq, 128)
+    vc_n = vc.cpu().numpy().reshape(M, layers, nkv, max_seq, 128)
+    for m in range(M):
+        qr = oracle.rope(oracle.head_norm(qkv[m, :nq * 128], qn, nq, 128), nq, 128, int(pos[m]))
+        kr = oracle.rope(oracle.head_norm(qkv[m, nq * 128:(nq + nkv) * 128], kn, nkv, 128), nkv, 128, int(pos[m]))
+        assert np.allclose(q[m].cpu().numpy(), qr, rtol=1e-4, atol=2e-4)
+        assert np.allclose(kc_n[m, layer, :, pos[m]].astype(np.float32).reshape(-1), kr, rtol=2e-3, atol=2e-3)
+        assert np.array_equal(vc_n[m, layer, :, pos[m]].reshape(-1), qkv[m, (nq + nkv) * 128:].astype(np.float16))
+    assert not kc_n[:, 0].any() and kc_n[0, layer, :, 1:].sum() == 0  # nothing else was touched
+
+    V, H = 300, 256
+    table = synth.activations_f16(V, H, 403)
+    toks = np.array([0, 299, 123], np.int32)
+    x = torch.empty((M, H), dtype=torch.float32, device="cuda")
+    k.embed_gather_f16(x, to_dev(table.view(np.uint16)), to_dev(toks), H, V, M)
+    assert np.array_equal(x.cpu().numpy(), table[toks].astype(np.float32))
+
+    Vv = 151643
+    logits = synth.rng(404).normal(size=(M, Vv)).astype(np.float32)
+    logits[1, 77] = logits[1].max()  # tie -> lowest index
+    ids = torch.zeros(M, dtype=torch.int32, device="cuda")
+    p = to_dev(pos)
+    for _ in range(2):  # twice: the tickets are reset by the kernel
+        k.sample_argmax_batched(to_dev(logits), Vv, Vv, M, ids, p)
+    assert [int(i) for i in ids.cpu()] == [oracle.argmax(logits[m]) for m in range(M)]
+    assert np.array_equal(p.cpu().numpy(), pos + 2)
+
+
+def test_gemv_decode_entry_residual_and_strides(cuda):
+    import torch
+
+    from blackwell_b200 import kernels as k
+
+    M, K, N = 3, 416, 200
+    W, sc16, _ = synth.int4_weights(N, K, 410)
+    gu = synth.activations_f16(M, 2 * K, 411).astype(np.float32)
+    res = synth.activations_f16(M, N + 8, 412).astype(np.float32)
+    y = to_dev(res.copy())
+    gud = to_dev(gu)
+    k.gemv_w4a8_decode(y, N + 8, y, gud, gud[:, K:], 2 * K, None, 0.0, to_dev(W), to_dev(sc16.view(np.uint16)), K, N,
+                       M)
+    act = oracle.swiglu(np.ascontiguousarray(gu[:, :K]), np.ascontiguousarray(gu[:, K:]))
+    ref = res[:, :N] + cpu_gemv(act, W, sc16)
+    out = y.cpu().numpy()
+    assert max_abs_rel(out[:, :N], ref) < 1e-3
+    assert np.array_equal(out[:, N:], res[:, N:])  # the padding columns are untouched
