@@ -324,6 +324,15 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         barrier()
 
+    # ---- the synthetic Qwen3-8B-shape decode step (configs[3]): batch 1 and 8, context 2048, reported beside the
+    # headline; tensor-parallel over all ranks when N > 1
+    decode = []
+    if not args.only and not args.no_decode:
+        for b in (1, 8):
+            try:
+                decode.append(run_decode(shapes.QWEN3_8B, b, 2048, 20, dev, world, rank))
+            except Exception as exc:  # the headline must survive a failure of the side measurement
+                decode.append({"model": shapes.QWEN3_8B.name, "batch": b, "error": repr(exc)[:200]})
     if rank != 0:
         return
     peak, peak_kind = measured_peak()
@@ -353,8 +362,64 @@ def run_ours(args, rank, world, local_rank):
                      "kernel": "gemv_w4_stream_kernel<1,half>", "nominal_frac": achieved / 8000.0},
         "cpu_baseline": cpu,
         "per_matrix": per,
+        "decode": decode,
     }
     print(json.dumps(line), flush=True)
+
+
+def run_decode(shape, batch, ctx, steps, dev, world=1, rank=0, max_seq=None):
+    """Times the synthetic decode step (one CUDA graph per step) with the cache pre-filled to ``ctx``; returns a
+    dict with tokens/s over all sequences and the HBM roofline fraction of the step."""
+    import torch
+
+    from blackwell_b200.decode import DecodeEngine
+
+    max_seq = max_seq or (ctx + 64)
+    eng = DecodeEngine(shape, batch, max_seq, dev, seed=3, world=world, rank=rank)
+    eng.fill_cache(ctx)
+    gen = torch.Generator(device="cpu")
+    gen.manual_seed(11)
+    eng.set_tokens(torch.randint(0, shape.vocab, (batch,), generator=gen))
+    eng.step()
+    torch.cuda.synchronize()
+    eng.pos.fill_(ctx - 1)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        eng.step()
+    for _ in range(3):
+        eng.pos.fill_(ctx - 1)
+        graph.replay()
+    torch.cuda.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(steps):
+        eng.pos.fill_(ctx - 1)  # every timed step attends over the same context length
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = float(np.median(times))
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    peak, kind = measured_peak()
+    nbytes = eng.step_bytes(ctx)  # per rank
+    out = {"model": shape.name, "batch": batch, "ctx": ctx, "tp": world, "ms_per_step": round(ms, 4),
+           "tok_s": round(batch / (ms / 1e3), 1), "hbm_bytes_per_step_per_gpu": nbytes,
+           "gbs_per_gpu": round(nbytes / ms / 1e6, 1), "roofline_frac": round(nbytes / ms / 1e6 / peak, 3),
+           "peak_kind": kind, "kv": "f16", "status": 0}
+    from blackwell_b200 import kernels as k
+
+    out["status"] = k.device_status()
+    del eng, graph
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -365,6 +430,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying "
                     "a captured CUDA graph")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode-step side measurement")
+    ap.add_argument("--decode-only", default=None, help="profiling aid: only the decode step, MODEL:BATCH:CTX "
+                    "(MODEL = 8b or 32b); prints its own JSON line")
     ap.add_argument("--only", default=None, help="profiling aid: run one matrix of the set, NAME or NAME:ROWS")
     ap.add_argument("--tune", default=None, help="profiling aid: comma list of key=value for bw_set_tuning")
     args = ap.parse_args()
@@ -377,6 +445,23 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.decode_only:
+        import torch
+
+        model, b, c = args.decode_only.split(":")
+        if world > 1:
+            import torch.distributed as dist
+
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        torch.cuda.set_device(local_rank)
+        shape = shapes.QWEN3_8B if model == "8b" else shapes.QWEN3_32B
+        out = run_decode(shape, int(b), int(c), args.steps, torch.device("cuda", local_rank), world, rank)
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
         return
     if world > 1:
         import torch

@@ -1,0 +1,127 @@
+// INT4-weight x INT8-activation block-16 GEMM for batches of 9..64 sequences on the 5th-generation tensor cores
+// (tcgen05.mma kind::i8, accumulators in tensor memory).  Device side.
+//
+//   y[m][n] = sum_kb dot16(W[n,kb], xq[m,kb]) * w_sc[n,kb] * x_sc[m,kb]
+//
+// The scale changes every 16 k, the MMA consumes 32 k: each k-block gets its own MMA whose A operand holds the
+// block in its first 16-byte K core matrix and a shared all-zero core matrix in the second (the descriptor's
+// leading-dimension offset points the second K step at the zero region), so every accumulator tile is the exact
+// int32 dot product of ONE k-block.  Accumulator tiles start from the bit pattern of 1.5 * 2^23, so the value
+// read back is a float holding 12582912 + 16 * dot exactly and the per-block scaling is two FMAs per
+// (row, sequence, block): t = fma(F, w_sc, -12582912 * w_sc) (exact for binary16 scales), acc = fma(t, x_sc/16, acc).
+//
+// Roles inside a CTA of 12 warps (one CTA works on 128 weight rows x a range of 256-k chunks):
+//   warp 0      producer: TMA 2-D loads of packed nibbles and weight scales, bulk copies of the activations
+//   warp 1      MMA issuer (one elected lane)
+//   warps 4-7   epilogue: tcgen05.ld, scaling, fp32 accumulation in registers, refill of the tile with the
+//               magic pattern, final store (thread = weight row = TMEM lane)
+//   warps 8-11  unpack: nibbles -> signed bytes 16*q in the K-major core-matrix layout the MMA reads
+// All waits are bounded; a wait that gives up raises an abort flag that every role polls.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace bw {
+namespace tc {
+
+constexpr int kKc = 256;          // k per chunk = 16 k-blocks
+constexpr int kBlocksPerChunk = 16;
+constexpr int kRows = 128;        // weight rows per CTA tile = MMA M
+constexpr int kSP = 3;            // packed-nibble ring slots
+constexpr int kSA = 2;            // operand (A int8 + B) ring slots
+constexpr int kSS = 4;            // scale ring slots
+constexpr int kABlockStride = 2048 + 16;  // bytes between the int8 tiles of consecutive k-blocks (odd 16-byte count
+                                          // spreads the unpack stores over the shared-memory banks)
+constexpr int kPackedBytes = kRows * (kKc / 2);                  // 16384
+constexpr int kWScaleBytes = kRows * kBlocksPerChunk * 2;        // 4096
+constexpr int kAStageBytes = kBlocksPerChunk * kABlockStride;    // 33024
+constexpr int kZeroBytes = 2048;
+constexpr int kThreads = 384;
+
+struct TcArgs {
+    float* y;                 // [M][y_stride]
+    const float* residual;    // optional, same layout as y
+    long y_stride;
+    const unsigned char* xb;  // activations in chunk layout (see prep kernel)
+    const __half* Wsc;        // [N][nkb] weight scales
+    int nkb;                  // K / 16
+    float* partial;           // [tiles][ksplit][Mpad][128] when ksplit > 1
+    unsigned int* tickets;    // [tiles], zero before and after the call
+    int N, M, Mpad;           // Mpad = MMA N in {16, 32, 64}
+    int nchunks;              // ceil(K / 256)
+    int ksplit;               // CTAs sharing one row tile
+};
+
+// bytes of one activation chunk in global memory: 16 blocks x Mpad rows x 16 B, then 16 x Mpad block scales
+__host__ __device__ inline size_t xb_chunk_bytes(int Mpad) { return (size_t)kBlocksPerChunk * Mpad * 16 + (size_t)kBlocksPerChunk * Mpad * 4; }
+
+// ------------------------------------------------------------------ tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(1u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(addr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16_const(uint32_t addr, uint32_t c) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+        ::"r"(addr), "r"(c)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 2-D tiled TMA load (no multicast): box -> shared memory of this CTA, bytes counted on an mbarrier.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_g2s_plain(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: rows of a core matrix 16 B apart, 8-row groups `sbo`
+// bytes apart, the two 16-byte K steps of one MMA `lbo` bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+    return d;
+}
+// Instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, M = 128, N = n.
+__host__ __device__ inline uint32_t idesc_i8(int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+}
+
+}  // namespace tc
+}  // namespace bw

@@ -13,6 +13,13 @@
 
 namespace bw {
 
+namespace tc {  // tensor-core path, gemm_w4a8_tc.cu
+bool eligible(const GemvArgs& a, int M);
+cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st);
+int read_clear_status();
+void set_ksplit_override(int v);
+}  // namespace tc
+
 // --------------------------------------------------------------------------
 // Plain-load kernel: one warp per output row, lanes stride over k-blocks, up to
 // 8 sequences per pass.  Any K % 16 == 0, any N, 8-byte aligned weights.  Same
@@ -110,7 +117,7 @@ __global__ void __launch_bounds__(128) block_dots_kernel(int32_t* dots, const ui
 // --------------------------------------------------------------------------
 // Host side
 // --------------------------------------------------------------------------
-static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0}, g_tune_rg{0}, g_tune_threads{0};
+static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0}, g_tune_rg{0}, g_tune_threads{0}, g_tune_tc_min{0};
 static std::atomic<long long> g_launches{0};
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -259,11 +266,34 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
     if (!a.y || !a.W || !a.Wsc || !a.x) return cudaErrorInvalidValue;
     if (!aligned(a.W, 8) || !aligned(a.x, 8)) return cudaErrorInvalidValue;
     const bool prequant = (a.xkind == kXInt8 || a.xkind == kXInt4);
-    if (!prequant && (M > 8 || !aligned(a.x, 16))) return cudaErrorInvalidValue;
     a.nch = a.K / 32;
     if (a.x_stride <= 0) a.x_stride = a.K;
     if (a.y_stride <= 0) a.y_stride = a.N;
     if (a.x_stride % 4 != 0 || a.y_stride < a.N) return cudaErrorInvalidValue;
+    if (!prequant && !aligned(a.x, 16)) return cudaErrorInvalidValue;
+    // Batches above the dp4a kernel's range go to the tensor cores, up to 64 sequences per launch.
+    const int tc_min = g_tune_tc_min.load() > 0 ? g_tune_tc_min.load() : 9;
+    if (sizeof(WS) == 2 && M >= tc_min && tc::eligible(a, M < 64 ? M : 64)) {
+        for (int m0 = 0; m0 < M; m0 += 64) {
+            const int mc = (M - m0) < 64 ? (M - m0) : 64;
+            GemvArgs b = a;
+            b.y = a.y + (size_t)m0 * a.y_stride;
+            if (a.residual) b.residual = a.residual + (size_t)m0 * a.y_stride;
+            if (a.xkind == kXInt8) {
+                b.x = static_cast<const int8_t*>(a.x) + (size_t)m0 * a.K;
+                b.xsc = a.xsc + (size_t)m0 * (a.K / 16);
+            } else if (a.xkind == kXHalf) {
+                b.x = static_cast<const __half*>(a.x) + (size_t)m0 * a.x_stride;
+            } else {
+                b.x = static_cast<const float*>(a.x) + (size_t)m0 * a.x_stride;
+                if (a.x2) b.x2 = static_cast<const float*>(a.x2) + (size_t)m0 * a.x_stride;
+            }
+            cudaError_t e = tc::launch(b, mc, st);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
+    if (!prequant && M > 8) return cudaErrorInvalidValue;
     // M > 8: passes of up to 8 sequences (pre-quantized operands only).
     for (int m0 = 0; m0 < M; m0 += 8) {
         const int mc = (M - m0) < 8 ? (M - m0) : 8;
@@ -389,6 +419,8 @@ extern "C" int bw_device_status(int* status_out) {
         const int zero = 0;
         e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
     }
+    const int v2 = tc::read_clear_status();
+    if (v == 0 && v2 > 0) v = v2;
     if (status_out) *status_out = v;
     return e;
 }
@@ -400,6 +432,8 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 2: g_tune_force_plain = value; return 0;
         case 3: g_tune_rg = value; return 0;
         case 4: g_tune_threads = value; return 0;
+        case 5: g_tune_tc_min = value; return 0;
+        case 6: tc::set_ksplit_override(value); return 0;
         default: return cudaErrorInvalidValue;
     }
 }

@@ -38,7 +38,7 @@ enum XKind : int {
 };
 
 // Device status word of this translation unit (see bw_device_status).
-__device__ int g_status = 0;
+static __device__ int g_status = 0;
 
 struct XChunk {      // one 32-element activation chunk of one sequence
     uint32_t e[4];   // even-k bytes of weight word i
