@@ -193,7 +193,7 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     mats = gemv_set()
-    M = 1
+    M = args.batch
     if args.tune:
         for kv in args.tune.split(","):
             a, b = kv.split("=")
@@ -433,6 +433,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step side measurement")
     ap.add_argument("--decode-only", default=None, help="profiling aid: only the decode step, MODEL:BATCH:CTX "
                     "(MODEL = 8b or 32b); prints its own JSON line")
+    ap.add_argument("--batch", type=int, default=1, help="profiling aid: sequences per GEMV (the headline is 1)")
     ap.add_argument("--only", default=None, help="profiling aid: run one matrix of the set, NAME or NAME:ROWS")
     ap.add_argument("--tune", default=None, help="profiling aid: comma list of key=value for bw_set_tuning")
     args = ap.parse_args()

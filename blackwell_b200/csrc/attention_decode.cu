@@ -48,6 +48,7 @@ struct AttnArgs {
     int nsplit, split_len;
     float scale;
     float* part;           // [M][nqh][nsplit][130] when nsplit > 1
+    unsigned int* tickets; // [M][nkv] arrival counters (zero between calls): the last split CTA merges; or nullptr
 };
 
 // Partial record of one (sequence, head, split): 128 un-normalised outputs, then max and sum.
@@ -129,32 +130,71 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_split_kernel(cons
         __syncwarp();
     }
 
-    // merge the four warps
+    __shared__ int s_last;
+    // Combines the four warps' online-softmax states; writes the final output or this split's partial record.
+    auto merge_warps_and_emit = [&](bool final_out) {
 #pragma unroll
-    for (int h = 0; h < GQ; ++h) {
-        if (lane == 0) { s_m[warp][h] = mx[h]; s_l[warp][h] = l[h]; }
-        *reinterpret_cast<float4*>(&s_o[warp][h][4 * lane]) = o[h];
-    }
-    __syncthreads();
-    for (int idx = t; idx < GQ * kHd; idx += blockDim.x) {
-        const int h = idx / kHd, d = idx - h * kHd;
-        float mm = -FLT_MAX;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, s_m[w][h]);
-        float ls = 0.f, os = 0.f;
-#pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) {
-            const float c = __expf(s_m[w][h] - mm);
-            ls = fmaf(s_l[w][h], c, ls);
-            os = fmaf(s_o[w][h][d], c, os);
+        for (int h = 0; h < GQ; ++h) {
+            if (lane == 0) { s_m[warp][h] = mx[h]; s_l[warp][h] = l[h]; }
+            *reinterpret_cast<float4*>(&s_o[warp][h][4 * lane]) = o[h];
         }
-        const size_t head = (size_t)m * a.nqh + h0 + h;
-        if (a.nsplit == 1) {
-            a.out[head * kHd + d] = os * (1.0f / (ls + 1e-9f));
-        } else {
-            float* rec = a.part + (head * a.nsplit + split) * kPartStride;
-            rec[d] = os;
-            if (d == 0) { rec[kHd] = mm; rec[kHd + 1] = ls; }
+        __syncthreads();
+        for (int idx = t; idx < GQ * kHd; idx += blockDim.x) {
+            const int h = idx / kHd, d = idx - h * kHd;
+            float mm = -FLT_MAX;
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, s_m[w][h]);
+            float ls = 0.f, os = 0.f;
+#pragma unroll
+            for (int w = 0; w < kAttnWarps; ++w) {
+                const float c = __expf(s_m[w][h] - mm);
+                ls = fmaf(s_l[w][h], c, ls);
+                os = fmaf(s_o[w][h][d], c, os);
+            }
+            const size_t head = (size_t)m * a.nqh + h0 + h;
+            if (final_out) {
+                a.out[head * kHd + d] = os * (1.0f / (ls + 1e-9f));
+            } else {
+                float* rec = a.part + (head * a.nsplit + split) * kPartStride;
+                rec[d] = os;
+                if (d == 0) { rec[kHd] = mm; rec[kHd + 1] = ls; }
+            }
+        }
+    };
+    merge_warps_and_emit(a.nsplit == 1);
+
+    // With arrival counters the CTA that finishes a (sequence, kv head) last merges all its splits itself, each
+    // warp folding a quarter of the records into a fresh online-softmax state; no second launch.
+    if (a.nsplit > 1 && a.tickets) {
+        __threadfence();
+        __syncthreads();
+        if (t == 0) s_last = (atomicAdd(&a.tickets[m * a.nkv + kvh], 1u) == (unsigned)a.nsplit - 1) ? 1 : 0;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+#pragma unroll
+            for (int h = 0; h < GQ; ++h) {
+                mx[h] = -FLT_MAX; l[h] = 0.f; o[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float* base = a.part + ((size_t)m * a.nqh + h0 + h) * a.nsplit * kPartStride;
+                for (int s = warp; s < a.nsplit; s += kAttnWarps) {
+                    const float* rec = base + (size_t)s * kPartStride;
+                    const float ls = __ldcg(rec + kHd + 1);
+                    if (ls > 0.f) {
+                        const float ms = __ldcg(rec + kHd);
+                        const float2 r0 = __ldcg(reinterpret_cast<const float2*>(rec + 4 * lane));
+                        const float2 r1 = __ldcg(reinterpret_cast<const float2*>(rec + 4 * lane + 2));
+                        const float mnew = fmaxf(mx[h], ms);
+                        const float c0 = __expf(mx[h] - mnew), c1 = __expf(ms - mnew);
+                        o[h] = make_float4(o[h].x * c0 + r0.x * c1, o[h].y * c0 + r0.y * c1, o[h].z * c0 + r1.x * c1,
+                                           o[h].w * c0 + r1.y * c1);
+                        l[h] = l[h] * c0 + ls * c1;
+                        mx[h] = mnew;
+                    }
+                }
+            }
+            __syncthreads();
+            merge_warps_and_emit(true);
+            if (t == 0) a.tickets[m * a.nkv + kvh] = 0;
         }
     }
 }
@@ -213,6 +253,8 @@ static cudaError_t attn_scratch(size_t bytes, float** out) {
         size_t want = bytes < (size_t)(4 << 20) ? (size_t)(4 << 20) : bytes;
         cudaError_t e = cudaMalloc(&s.ptr, want);
         if (e != cudaSuccess) return e;
+        e = cudaMemset(s.ptr, 0, want);  // the arrival counters at the front must start at zero
+        if (e != cudaSuccess) return e;
         s.bytes = want;
     }
     *out = s.ptr;
@@ -240,9 +282,15 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     a.nsplit = nsplit;
     a.scale = 1.0f / sqrtf((float)kHd);
     a.part = nullptr;
+    a.tickets = nullptr;
     if (nsplit > 1) {
-        cudaError_t e = attn_scratch((size_t)a.M * a.nqh * nsplit * kPartStride * sizeof(float), &a.part);
+        // scratch = [arrival counters, one per (sequence, kv head)] [partial records]
+        const size_t tick_bytes = (((size_t)a.M * a.nkv * sizeof(unsigned int)) + 255) & ~(size_t)255;
+        float* base = nullptr;
+        cudaError_t e = attn_scratch(tick_bytes + (size_t)a.M * a.nqh * nsplit * kPartStride * sizeof(float), &base);
         if (e != cudaSuccess) return e;
+        a.tickets = reinterpret_cast<unsigned int*>(base);
+        a.part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(base) + tick_bytes);
     }
     const dim3 grid(nsplit, a.nkv, a.M);
     switch (gq) {
@@ -252,14 +300,7 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
         default: attn_decode_split_kernel<KVT, 8><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
     }
     count_launch(1);
-    cudaError_t e = cudaPeekAtLastError();
-    if (e != cudaSuccess) return e;
-    if (nsplit > 1) {
-        attn_merge_kernel<<<a.M * a.nqh, kHd, 0, st>>>(a.out, a.part, nsplit);
-        count_launch(1);
-        e = cudaPeekAtLastError();
-    }
-    return e;
+    return cudaPeekAtLastError();
 }
 
 }  // namespace bw

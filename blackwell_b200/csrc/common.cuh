@@ -49,14 +49,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // second of wall time and returns false; the caller then flags the status word
 // and leaves the kernel in an orderly way.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-#pragma unroll 1
-    for (int i = 0; i < 128; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
+    // The limit is counted on the SM's own cycle counter (cheap to read); the global nanosecond timer costs
+    // on the order of a microsecond per read, which would quantise every wake-up.
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
 #pragma unroll 1
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > 1000000000ull) return false;
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > 2500000000ll) return false;  // more than a second at any SM clock
     }
 }
 

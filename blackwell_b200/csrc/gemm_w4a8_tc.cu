@@ -61,31 +61,46 @@ __global__ void __launch_bounds__(256) prep_x_kernel(unsigned char* xb, const Ge
 // ----------------------------------------------------------------------------------------------------------
 // Shared memory map of the MMA kernel (offsets from the 1024-aligned base).
 // ----------------------------------------------------------------------------------------------------------
+// A TMA box brings 128 rows x (128 * SUB) bytes: SUB consecutive 256-k chunks of every row in one request, so
+// that DRAM sees 256- or 512-byte runs per row instead of 128-byte ones (which measured at a fifth of the
+// bandwidth).  Unpack, MMA and epilogue still work chunk by chunk.
+__host__ __device__ constexpr int sub_chunks(int Mpad) { return Mpad > 0 ? 2 : 2; }
+__host__ __device__ constexpr int packed_slots(int Mpad) { return Mpad <= 16 ? 3 : 2; }
+// The activation ring runs deeper than the operand ring: its slots are refilled from L2 only after the MMAs that
+// read them retire, and with two slots that latency was the period of the whole pipeline.
+__host__ __device__ constexpr int b_slots(int Mpad) { return Mpad <= 32 ? 4 : 3; }
+__host__ __device__ constexpr int s_slots(int Mpad) { return Mpad <= 32 ? 4 : 3; }
+__host__ __device__ constexpr int packed_slot_bytes(int Mpad) { return kRows * 128 * sub_chunks(Mpad); }
+
 struct Smem {
     static constexpr int kBars = 0;                                      // mbarriers, 8 B each
     static constexpr int kTmemPtr = 512;                                 // TMEM base address from tcgen05.alloc
     static constexpr int kAbort = 516;
     static constexpr int kLast = 520;
-    static constexpr int kPacked = 1024;                                 // kSP x 16 KB
-    static constexpr int kA = kPacked + kSP * kPackedBytes;              // kSA x 33,024 B
-    static constexpr int kZero = kA + kSA * kAStageBytes;                // 2 KB of zeros (after every A tile)
-    static constexpr int kB = kZero + kZeroBytes;                        // kSA x (16 blocks x Mpad x 16 B)
-    __host__ __device__ static int scales(int Mpad) { return kB + kSA * kBlocksPerChunk * Mpad * 16; }
-    __host__ __device__ static int scale_slot_bytes(int Mpad) { return kBlocksPerChunk * Mpad * 4; }  // x_sc / 16
-    __host__ __device__ static int total(int Mpad) { return scales(Mpad) + kSS * scale_slot_bytes(Mpad); }
+    static constexpr int kPacked = 1024;                                 // packed_slots x packed_slot_bytes
+    __host__ __device__ static constexpr int a_off(int Mpad) { return kPacked + packed_slots(Mpad) * packed_slot_bytes(Mpad); }
+    __host__ __device__ static constexpr int zero_off(int Mpad) { return a_off(Mpad) + kSA * kAStageBytes; }  // after every A tile
+    __host__ __device__ static constexpr int b_off(int Mpad) { return zero_off(Mpad) + kZeroBytes; }
+    __host__ __device__ static constexpr int scales(int Mpad) { return b_off(Mpad) + b_slots(Mpad) * kBlocksPerChunk * Mpad * 16; }
+    __host__ __device__ static constexpr int scale_slot_bytes(int Mpad) { return kBlocksPerChunk * Mpad * 4; }  // x_sc / 16
+    __host__ __device__ static constexpr int wscales(int Mpad) { return scales(Mpad) + s_slots(Mpad) * scale_slot_bytes(Mpad); }
+    __host__ __device__ static constexpr int total(int Mpad) { return wscales(Mpad) + kSW * kWScaleBytes; }  // weight-scale ring
 };
 // barrier indices
 enum : int {
-    kFullP = 0,                 // + slot (kSP): packed nibbles landed
-    kEmptyP = kFullP + kSP,     // packed slot unpacked
-    kReadyA = kEmptyP + kSP,    // + slot (kSA): int8 operand written
-    kFullB = kReadyA + kSA,     // activations landed
-    kFreeAB = kFullB + kSA,     // MMAs that read the slot have completed
-    kFullS = kFreeAB + kSA,     // + slot (kSS): scales landed
-    kEmptyS = kFullS + kSS,     // scales consumed by the epilogue
-    kDFull = kEmptyS + kSS,     // + group (2): accumulator group complete
-    kDEmpty = kDFull + 2,       // accumulator group drained and refilled
-    kNumBars = kDEmpty + 2,
+    kFullP = 0,                 // + slot (up to 4): packed nibbles landed
+    kEmptyP = kFullP + 4,       // packed slot unpacked
+    kReadyA = kEmptyP + 4,      // + slot (kSA): int8 operand written
+    kFreeAB = kReadyA + kSA,    // MMAs that read the operand slot have completed
+    kFullB = kFreeAB + kSA,     // + slot (up to 4): activations landed
+    kFreeB = kFullB + 4,        // MMAs that read the activation slot have completed
+    kFullS = kFreeB + 4,        // + slot (up to 4): scales landed
+    kEmptyS = kFullS + 4,       // scales consumed by the epilogue
+    kDFull = kEmptyS + 4,       // + group (2): accumulator group complete
+    kDEmpty = kDFull + 2,       // accumulator group read out
+    kFullW = kDEmpty + 2,       // + slot (kSW): weight scales of a chunk landed
+    kEmptyW = kFullW + kSW,     // weight scales consumed
+    kNumBars = kEmptyW + kSW,
 };
 
 template <int NMMA>
@@ -93,13 +108,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
     constexpr int GB = 256 / NMMA;                      // k-blocks per accumulator group (256 TMEM columns)
     constexpr int GPC = kBlocksPerChunk / GB;           // groups per chunk
+    constexpr int SUB = sub_chunks(NMMA), SPS = packed_slots(NMMA), PSLOT = packed_slot_bytes(NMMA);
+    constexpr int SB = b_slots(NMMA), SS = s_slots(NMMA);
     extern __shared__ __align__(1024) unsigned char smem[];
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-    const int tile = blockIdx.x / a.ksplit, kpart = blockIdx.x % a.ksplit;
-    const int c0 = (int)(((long long)a.nchunks * kpart) / a.ksplit);
-    const int c1 = (int)(((long long)a.nchunks * (kpart + 1)) / a.ksplit);
-    const int nloc = c1 - c0;
-    const int row0 = tile * kRows;
+    const int units = ((a.N + kRows - 1) / kRows) * a.ksplit;   // (row tile, K part) pairs, walked round-robin
+    auto unit_range = [&](int u, int& tile, int& kpart, int& c0, int& nloc) {
+        tile = u / a.ksplit;
+        kpart = u - tile * a.ksplit;
+        const int nsuper = (a.nchunks + SUB - 1) / SUB;  // K parts begin on box boundaries
+        c0 = SUB * (int)(((long long)nsuper * kpart) / a.ksplit);
+        const int c1 = min(a.nchunks, SUB * (int)(((long long)nsuper * (kpart + 1)) / a.ksplit));
+        nloc = c1 - c0;
+    };
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kAbort);
@@ -115,14 +136,16 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
     const int b_slot = kBlocksPerChunk * NMMA * 16;
 
     if (t == 0) {
-        for (int i = 0; i < kSP; ++i) { mbar_init(bar(kFullP + i), 1); mbar_init(bar(kEmptyP + i), 128); }
-        for (int i = 0; i < kSA; ++i) { mbar_init(bar(kReadyA + i), 128); mbar_init(bar(kFullB + i), 1); mbar_init(bar(kFreeAB + i), 1); }
-        for (int i = 0; i < kSS; ++i) { mbar_init(bar(kFullS + i), 1); mbar_init(bar(kEmptyS + i), 128); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(kDFull + i), 1); mbar_init(bar(kDEmpty + i), 128); }
+        for (int i = 0; i < 4; ++i) { mbar_init(bar(kFullP + i), 1); mbar_init(bar(kEmptyP + i), 4); }
+        for (int i = 0; i < kSA; ++i) { mbar_init(bar(kReadyA + i), 4); mbar_init(bar(kFreeAB + i), 1); }
+        for (int i = 0; i < 4; ++i) { mbar_init(bar(kFullB + i), 1); mbar_init(bar(kFreeB + i), 1); }
+        for (int i = 0; i < 4; ++i) { mbar_init(bar(kFullS + i), 1); mbar_init(bar(kEmptyS + i), 8); }
+        for (int i = 0; i < kSW; ++i) { mbar_init(bar(kFullW + i), 64); mbar_init(bar(kEmptyW + i), 8); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(kDFull + i), 1); mbar_init(bar(kDEmpty + i), 8); }
         *abort_flag = 0;
         mbar_fence_init();
     }
-    for (int i = t; i < kZeroBytes / 4; i += kThreads) reinterpret_cast<uint32_t*>(smem + Smem::kZero)[i] = 0u;
+    for (int i = t; i < kZeroBytes / 4; i += kThreads) reinterpret_cast<uint32_t*>(smem + Smem::zero_off(NMMA))[i] = 0u;
     if (warp == 0) {
         tmem_alloc(smem_u32(smem + Smem::kTmemPtr), 512);
         tmem_relinquish();
@@ -133,84 +156,139 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
     tc_fence_after();
     const uint32_t tmem = *tmem_ptr;
 
-    if (warp >= 4 && warp < 8) {
-        // every accumulator column of this thread's lane starts at the magic pattern
-        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        for (int c = 0; c < 512; c += 16) tmem_st16_const(lane_addr + c, (uint32_t)kMagicInt);
-        tmem_wait_st();
-        tc_fence_before();
-    }
-    __syncthreads();
-    tc_fence_after();
-
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ producer
         if (lane == 0) {
-            for (int i = 0; i < nloc; ++i) {
-                const int c = c0 + i;
-                const int sp = i % kSP, sa = i % kSA, ss = i % kSS;
-                if (!wait(kEmptyS + ss, ((i / kSS) & 1) ^ 1)) break;
-                unsigned char* sslot = smem + s_off + ss * s_slot;
-                mbar_expect_tx(bar(kFullS + ss), s_slot);
-                const unsigned char* xchunk = a.xb + (size_t)c * xb_chunk_bytes(NMMA);
-                bulk_g2s_plain(smem_u32(sslot), xchunk + b_slot, s_slot, bar(kFullS + ss));
-                if (!wait(kEmptyP + sp, ((i / kSP) & 1) ^ 1)) break;
-                mbar_expect_tx(bar(kFullP + sp), kPackedBytes);
-                tma_load_2d(smem_u32(smem + Smem::kPacked + sp * kPackedBytes), &map_w, c * (kKc / 2), row0, bar(kFullP + sp));
-                if (!wait(kFreeAB + sa, ((i / kSA) & 1) ^ 1)) break;
-                mbar_expect_tx(bar(kFullB + sa), b_slot);
-                bulk_g2s_plain(smem_u32(smem + Smem::kB + sa * b_slot), xchunk, b_slot, bar(kFullB + sa));
+            int n = 0, np = 0;  // chunks / boxes issued so far by this CTA: ring slots and phases follow them
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                int tile, kpart, c0, nloc;
+                unit_range(u, tile, kpart, c0, nloc);
+                const int row0 = tile * kRows;
+                for (int i = 0; i < nloc; ++i, ++n) {
+                    const int c = c0 + i;
+                    const int sb = n % SB, ss = n % SS;
+                    if (!wait(kEmptyS + ss, ((n / SS) & 1) ^ 1)) { ok = false; break; }
+                    unsigned char* sslot = smem + s_off + ss * s_slot;
+                    const unsigned char* xchunk = a.xb + (size_t)c * xb_chunk_bytes(NMMA);
+                    if (a.debug & 16) mbar_arrive(bar(kFullS + ss));
+                    else {
+                    mbar_expect_tx(bar(kFullS + ss), s_slot);
+                    bulk_g2s_plain(smem_u32(sslot), xchunk + b_slot, s_slot, bar(kFullS + ss));
+                    }
+                    if (i % SUB == 0) {  // a new box: SUB chunks of packed nibbles at once
+                        const int sp = np % SPS;
+                        if (!wait(kEmptyP + sp, ((np / SPS) & 1) ^ 1)) { ok = false; break; }
+                        if (a.debug & 32) mbar_arrive(bar(kFullP + sp));
+                        else {
+                        mbar_expect_tx(bar(kFullP + sp), PSLOT);
+                        tma_load_2d(smem_u32(smem + Smem::kPacked + sp * PSLOT), &map_w, c * (kKc / 2) / a.map_elem,
+                                    row0, bar(kFullP + sp));
+                        }
+                        ++np;
+                    }
+                    if (!wait(kFreeB + sb, ((n / SB) & 1) ^ 1)) { ok = false; break; }
+                    if (a.debug & 16) mbar_arrive(bar(kFullB + sb));
+                    else {
+                    mbar_expect_tx(bar(kFullB + sb), b_slot);
+                    bulk_g2s_plain(smem_u32(smem + Smem::b_off(NMMA) + sb * b_slot), xchunk, b_slot, bar(kFullB + sb));
+                    }
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = idesc_i8(NMMA);
-            const uint32_t zero_addr = smem_u32(smem + Smem::kZero);
-            int gcount = 0;
-            for (int i = 0; i < nloc; ++i) {
-                const int sa = i % kSA;
-                const uint32_t par = (i / kSA) & 1;
-                if (!wait(kReadyA + sa, par)) break;
-                if (!wait(kFullB + sa, par)) break;
-                tc_fence_after();
-                const uint32_t a_base = smem_u32(smem + Smem::kA + sa * kAStageBytes);
-                const uint32_t b_base = smem_u32(smem + Smem::kB + sa * b_slot);
-                bool ok = true;
-                for (int g = 0; g < GPC && ok; ++g, ++gcount) {
-                    const int dg = gcount & 1;
-                    if (!wait(kDEmpty + dg, ((gcount >> 1) & 1) ^ 1)) { ok = false; break; }
+            const uint32_t zero_addr = smem_u32(smem + Smem::zero_off(NMMA));
+            int gcount = 0, n = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                int tile, kpart, c0, nloc;
+                unit_range(u, tile, kpart, c0, nloc);
+                for (int i = 0; i < nloc && ok; ++i, ++n) {
+                    const int sa = n % kSA, sb = n % SB;
+                    if (!wait(kReadyA + sa, (n / kSA) & 1)) { ok = false; break; }
+                    if (!wait(kFullB + sb, (n / SB) & 1)) { ok = false; break; }
                     tc_fence_after();
-                    for (int bi = 0; bi < GB; ++bi) {
-                        const int b = g * GB + bi;
-                        const uint32_t a_addr = a_base + b * kABlockStride;
-                        // A: first K step = the block, second K step = the zero region
-                        const uint64_t da = smem_desc(a_addr, zero_addr - a_addr, 128);
-                        // B: first K step = the block; the second multiplies zeros, any valid rows will do
-                        const uint32_t b_addr = b_base + b * NMMA * 16;
-                        const uint64_t db = smem_desc(b_addr, b == kBlocksPerChunk - 1 ? 0 : NMMA * 16, 128);
-                        tc_mma_i8(tmem + dg * 256 + bi * NMMA, da, db, idesc);
+                    const uint32_t a_base = smem_u32(smem + Smem::a_off(NMMA) + sa * kAStageBytes);
+                    const uint32_t b_base = smem_u32(smem + Smem::b_off(NMMA) + sb * b_slot);
+                    for (int g = 0; g < GPC && ok; ++g, ++gcount) {
+                        const int dg = gcount & 1;
+                        if (!wait(kDEmpty + dg, ((gcount >> 1) & 1) ^ 1)) { ok = false; break; }
+                        tc_fence_after();
+                        for (int bi = 0; bi < GB; ++bi) {
+                            if (a.debug & 4) break;
+                            const int b = g * GB + bi;
+                            const uint32_t a_addr = a_base + b * kABlockStride;
+                            // A: first K step = the block, second K step = the zero region
+                            const uint64_t da = smem_desc(a_addr, zero_addr - a_addr, 128);
+                            // B: first K step = the block; the second multiplies zeros, any valid rows will do
+                            const uint32_t b_addr = b_base + b * NMMA * 16;
+                            const uint64_t db = smem_desc(b_addr, b == kBlocksPerChunk - 1 ? 0 : NMMA * 16, 128);
+                            tc_mma_i8(tmem + dg * 256 + bi * NMMA, da, db, idesc, 0u);
+                        }
+                        tc_commit(bar(kDFull + dg));
                     }
-                    tc_commit(bar(kDFull + dg));
+                    if (ok) {
+                        tc_commit(bar(kFreeAB + sa));
+                        tc_commit(bar(kFreeB + sb));
+                    }
                 }
-                if (!ok) break;
-                tc_commit(bar(kFreeAB + sa));
             }
         }
-    } else if (warp >= 8) {
+    } else if (warp == 2 || warp == 3) {
+        // ------------------------------------------------------------------------------------ weight-scale loader
+        // The 16 scales of a row for one chunk are 32 bytes at a row pitch that is only 4-byte aligned in general, so
+        // they come through 4-byte cp.async copies (zero-filled past the end of K), two rows per thread, eight
+        // chunks ahead of the epilogue; completion is signalled on the slot's mbarrier by the copies themselves.
+        const int lt = t - 64;  // 0..63
+        int n = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            int tile, kpart, c0, nloc;
+            unit_range(u, tile, kpart, c0, nloc);
+            for (int i = 0; i < nloc; ++i, ++n) {
+                const int sw = n % kSW;
+                if (!wait(kEmptyW + sw, ((n / kSW) & 1) ^ 1)) { ok = false; break; }
+                unsigned char* slot = smem + Smem::wscales(NMMA) + sw * kWScaleBytes;
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int r = lt * 2 + rr;
+                    const int grow = min(tile * kRows + r, a.N - 1);
+                    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.Wsc + (size_t)grow * a.nkb) + (c0 + i) * 8;
+                    const uint32_t dst = smem_u32(slot + r * 32);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const bool in = 2 * ((c0 + i) * 8 + q) < a.nkb;
+                        cp_async4(dst + 4 * q, in ? src + q : src, in ? 4u : 0u);
+                    }
+                }
+                cp_async_arrive(bar(kFullW + sw));
+            }
+        }
+    } else if (warp >= 12) {
         // ------------------------------------------------------------------------------------ unpack
-        const int ut = t - 256;  // 0..127
-        for (int i = 0; i < nloc; ++i) {
-            const int sp = i % kSP, sa = i % kSA;
-            if (!wait(kFullP + sp, (i / kSP) & 1)) break;
-            if (!wait(kFreeAB + sa, ((i / kSA) & 1) ^ 1)) break;
-            const unsigned char* src = smem + Smem::kPacked + sp * kPackedBytes;
-            unsigned char* dst = smem + Smem::kA + sa * kAStageBytes;
+        const int ut = t - 384;  // 0..127
+        int n = 0, np = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+          int tile, kpart, c0, nloc;
+          unit_range(u, tile, kpart, c0, nloc);
+          for (int i = 0; i < nloc; ++i, ++n) {
+            const int sub = i % SUB, sa = n % kSA;
+            if (sub == 0) ++np;
+            const int sp = (np - 1) % SPS;
+            if (sub == 0 && !wait(kFullP + sp, ((np - 1) / SPS) & 1)) { ok = false; break; }
+            if (!wait(kFreeAB + sa, ((n / kSA) & 1) ^ 1)) { ok = false; break; }
+            const unsigned char* src = smem + Smem::kPacked + sp * PSLOT + sub * 128;
+            unsigned char* dst = smem + Smem::a_off(NMMA) + sa * kAStageBytes;
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
+                if (a.debug & 2) break;
                 const int gidx = it * 128 + ut;       // 16-byte chunk of the packed tile
                 const int row = gidx >> 3, cc = gidx & 7;
-                const uint4 w = *reinterpret_cast<const uint4*>(src + gidx * 16);
+                const uint4 w = *reinterpret_cast<const uint4*>(src + row * (128 * SUB) + cc * 16);
                 uint4 o0, o1;
                 nibbles_to_s8x16(w.x, o0.x, o0.y);
                 nibbles_to_s8x16(w.y, o0.z, o0.w);
@@ -220,111 +298,134 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                 *reinterpret_cast<uint4*>(d0) = o0;
                 *reinterpret_cast<uint4*>(d0 + kABlockStride) = o1;
             }
+            // one arrival per warp: hundreds of per-thread arrivals on one barrier serialise in shared memory
             fence_proxy_async();
-            mbar_arrive(bar(kReadyA + sa));
-            mbar_arrive(bar(kEmptyP + sp));
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bar(kReadyA + sa));
+                if (sub == SUB - 1 || i == nloc - 1) mbar_arrive(bar(kEmptyP + sp));  // the box is used up
+            }
+          }
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------------------------------ epilogue
+        constexpr int CW = NMMA / 2;                            // sequences (columns of a block) per thread
+        const int half = (warp - 4) >> 2;                       // 0: sequences [0, CW), 1: [CW, NMMA)
         const int row = (warp & 3) * 32 + lane;                 // weight row of the tile = TMEM lane
-        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        float acc[NMMA];
-#pragma unroll
-        for (int j = 0; j < NMMA; ++j) acc[j] = 0.f;
-        int gcount = 0;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + half * CW;
+        int gcount = 0, n = 0;
         bool ok = true;
-        // Weight scales of this thread's row come straight from global memory (a row's scales are only 4-byte
-        // aligned in general, which rules out bulk copies); the next chunk's 16 are fetched while the current
-        // chunk is scaled.  Blocks past the end of K read as scale 0.
-        const int grow_s = min(row0 + row, a.N - 1);
-        const uint32_t* wrow = reinterpret_cast<const uint32_t*>(a.Wsc + (size_t)grow_s * a.nkb);
-        uint32_t wnext[8];
-        auto fetch_scales = [&](int c) {
+        for (int u = blockIdx.x; u < units; u += gridDim.x) {
+            int tile, kpart, c0, nloc;
+            unit_range(u, tile, kpart, c0, nloc);
+            const int row0 = tile * kRows;
+            float acc[CW];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int b2 = c * 8 + q;  // pair index
-                wnext[q] = (2 * b2 < a.nkb) ? __ldg(wrow + b2) : 0u;
-            }
-        };
-        if (nloc > 0) fetch_scales(c0);
-        for (int i = 0; i < nloc && ok; ++i) {
-            const int ss = i % kSS;
-            float wsc[kBlocksPerChunk];
+            for (int j = 0; j < CW; ++j) acc[j] = 0.f;
+            for (int i = 0; i < nloc && ok; ++i, ++n) {
+                const int ss = n % SS;
+                const int sw = n % kSW;
+                if (!wait(kFullW + sw, (n / kSW) & 1)) { ok = false; break; }
+                uint32_t wcur[8];
+                {
+                    const uint4* wp = reinterpret_cast<const uint4*>(smem + Smem::wscales(NMMA) + sw * kWScaleBytes + row * 32);
+                    const uint4 w0 = wp[0], w1 = wp[1];
+                    wcur[0] = w0.x; wcur[1] = w0.y; wcur[2] = w0.z; wcur[3] = w0.w;
+                    wcur[4] = w1.x; wcur[5] = w1.y; wcur[6] = w1.z; wcur[7] = w1.w;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kEmptyW + sw));
+                if (!wait(kFullS + ss, (n / SS) & 1)) { ok = false; break; }
+                const float* sx = reinterpret_cast<const float*>(smem + s_off + ss * s_slot) + half * CW;
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wnext[q]));
-                wsc[2 * q] = f.x; wsc[2 * q + 1] = f.y;
-            }
-            if (i + 1 < nloc) fetch_scales(c0 + i + 1);
-            if (!wait(kFullS + ss, (i / kSS) & 1)) break;
-            const float* sx = reinterpret_cast<const float*>(smem + s_off + ss * s_slot);
+                for (int g = 0; g < GPC; ++g) {
+                    const int dg = gcount & 1;
+                    if (!wait(kDFull + dg, (gcount >> 1) & 1)) { ok = false; break; }
+                    ++gcount;
+                    tc_fence_after();
+                    // blocks of the group in pairs: two loads in flight per wait
 #pragma unroll
-            for (int g = 0; g < GPC; ++g, ++gcount) {
-                const int dg = gcount & 1;
-                if (!wait(kDFull + dg, (gcount >> 1) & 1)) { ok = false; break; }
-                tc_fence_after();
+                    for (int bi = 0; bi < GB; bi += 2) {
+                        uint32_t v[2][CW];
 #pragma unroll
-                for (int bi = 0; bi < GB; ++bi) {
-                    const int b = g * GB + bi;
-                    const float w = wsc[b];
-                    const float cneg = -kMagicFloat * w;       // exact: a binary16 scale times 1.5 * 2^23
+                        for (int p = 0; p < 2; ++p) {
+                            if (a.debug & 8) break;
+                            const uint32_t addr = lane_addr + dg * 256 + (bi + p) * NMMA;
+                            if constexpr (CW == 8) {
+                                tmem_ld8(addr, v[p]);
+                            } else {
 #pragma unroll
-                    for (int cb = 0; cb < NMMA; cb += 16) {
-                        uint32_t v[16];
-                        tmem_ld16(lane_addr + dg * 256 + bi * NMMA + cb, v);
+                                for (int c = 0; c < CW; c += 16)
+                                    tmem_ld16(addr + c, *reinterpret_cast<uint32_t(*)[16]>(&v[p][c]));
+                            }
+                        }
                         tmem_wait_ld();
+                        if (bi == GB - 2) {  // the whole group is in registers: the MMA warp may overwrite it
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar(kDEmpty + dg));
+                        }
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float4 s4 = *reinterpret_cast<const float4*>(sx + b * NMMA + cb + 4 * q);
-                            acc[cb + 4 * q + 0] = fmaf(fmaf(__uint_as_float(v[4 * q + 0]), w, cneg), s4.x, acc[cb + 4 * q + 0]);
-                            acc[cb + 4 * q + 1] = fmaf(fmaf(__uint_as_float(v[4 * q + 1]), w, cneg), s4.y, acc[cb + 4 * q + 1]);
-                            acc[cb + 4 * q + 2] = fmaf(fmaf(__uint_as_float(v[4 * q + 2]), w, cneg), s4.z, acc[cb + 4 * q + 2]);
-                            acc[cb + 4 * q + 3] = fmaf(fmaf(__uint_as_float(v[4 * q + 3]), w, cneg), s4.w, acc[cb + 4 * q + 3]);
+                        for (int p = 0; p < 2; ++p) {
+                            if (a.debug & 1) break;
+                            const int b = g * GB + bi + p;              // k-block within the chunk
+                            const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&wcur[b >> 1]));
+                            const float w = (b & 1) ? wf.y : wf.x;
+                            const float cn = -kMagicFloat * w;          // exact: a binary16 scale times 1.5 * 2^23
+#pragma unroll
+                            for (int q = 0; q < CW / 4; ++q) {
+                                const float4 s4 = *reinterpret_cast<const float4*>(sx + b * NMMA + 4 * q);
+                                const float f0 = __int_as_float((int)v[p][4 * q + 0] + kMagicInt);
+                                const float f1 = __int_as_float((int)v[p][4 * q + 1] + kMagicInt);
+                                const float f2 = __int_as_float((int)v[p][4 * q + 2] + kMagicInt);
+                                const float f3 = __int_as_float((int)v[p][4 * q + 3] + kMagicInt);
+                                acc[4 * q + 0] = fmaf(fmaf(f0, w, cn), s4.x, acc[4 * q + 0]);
+                                acc[4 * q + 1] = fmaf(fmaf(f1, w, cn), s4.y, acc[4 * q + 1]);
+                                acc[4 * q + 2] = fmaf(fmaf(f2, w, cn), s4.z, acc[4 * q + 2]);
+                                acc[4 * q + 3] = fmaf(fmaf(f3, w, cn), s4.w, acc[4 * q + 3]);
+                            }
                         }
                     }
                 }
-                // hand the group back holding the magic pattern again
-#pragma unroll
-                for (int c = 0; c < 256; c += 16) tmem_st16_const(lane_addr + dg * 256 + c, (uint32_t)kMagicInt);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(bar(kDEmpty + dg));
+                __syncwarp();
+                if (ok && lane == 0) mbar_arrive(bar(kEmptyS + ss));
             }
-            if (ok) mbar_arrive(bar(kEmptyS + ss));
-        }
 
-        // ---- results: straight to y, or through the K-split partial buffer with a last-arriver sum
-        const int grow = row0 + row;
-        if (a.ksplit == 1) {
-            if (grow < a.N && !*abort_flag) {
+            // ---- results: straight to y, or through the K-split partial buffer with a last-arriver sum
+            const int grow = row0 + row;
+            const int mbase = half * CW;
+            if (a.ksplit == 1) {
+                if (grow < a.N && ok && !*abort_flag) {
 #pragma unroll
-                for (int m = 0; m < NMMA; ++m)
-                    if (m < a.M) {
-                        const size_t yi = (size_t)m * a.y_stride + grow;
-                        a.y[yi] = a.residual ? acc[m] + a.residual[yi] : acc[m];
-                    }
-            }
-        } else {
-            float* mine = a.partial + ((size_t)(tile * a.ksplit + kpart) * NMMA) * kRows;
-#pragma unroll
-            for (int m = 0; m < NMMA; ++m) mine[m * kRows + row] = acc[m];
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            volatile int* last = reinterpret_cast<volatile int*>(smem + Smem::kLast);
-            if (t == 128) *last = (atomicAdd(&a.tickets[tile], 1u) == (unsigned)a.ksplit - 1) ? 1 : 0;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (*last) {
-                __threadfence();
-                if (grow < a.N && !*abort_flag) {
-                    for (int m = 0; m < a.M; ++m) {
-                        float sum = 0.f;
-                        for (int p = 0; p < a.ksplit; ++p)
-                            sum += __ldcg(a.partial + ((size_t)(tile * a.ksplit + p) * NMMA + m) * kRows + row);
-                        const size_t yi = (size_t)m * a.y_stride + grow;
-                        a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
-                    }
+                    for (int j = 0; j < CW; ++j)
+                        if (mbase + j < a.M) {
+                            const size_t yi = (size_t)(mbase + j) * a.y_stride + grow;
+                            a.y[yi] = a.residual ? acc[j] + a.residual[yi] : acc[j];
+                        }
                 }
-                if (t == 128) a.tickets[tile] = 0;
+            } else {
+                float* mine = a.partial + ((size_t)(tile * a.ksplit + kpart) * NMMA) * kRows;
+#pragma unroll
+                for (int j = 0; j < CW; ++j) mine[(mbase + j) * kRows + row] = acc[j];
+                __threadfence();
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                volatile int* last = reinterpret_cast<volatile int*>(smem + Smem::kLast);
+                if (t == 128) *last = (atomicAdd(&a.tickets[tile], 1u) == (unsigned)a.ksplit - 1) ? 1 : 0;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (*last) {
+                    __threadfence();
+                    if (grow < a.N && !*abort_flag) {
+                        for (int j = 0; j < CW && mbase + j < a.M; ++j) {
+                            float sum = 0.f;
+                            for (int p = 0; p < a.ksplit; ++p)
+                                sum += __ldcg(a.partial + ((size_t)(tile * a.ksplit + p) * NMMA + mbase + j) * kRows + row);
+                            const size_t yi = (size_t)(mbase + j) * a.y_stride + grow;
+                            a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
+                        }
+                    }
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (t == 128) a.tickets[tile] = 0;
+                }
             }
         }
     }
@@ -386,7 +487,9 @@ static cudaError_t tc_scratch(size_t bytes, unsigned char** out) {
 }
 
 static int g_tc_ksplit_override = 0;
+static int g_tc_debug = 0;
 void set_ksplit_override(int v) { g_tc_ksplit_override = v; }
+void set_debug(int v) { g_tc_debug = v; }
 
 int read_clear_status() {
     int v = 0;
@@ -441,11 +544,13 @@ cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st) {
     if (e != cudaSuccess) return e;
 
     CUtensorMap map_w;
-    const cuuint64_t dims[2] = {(cuuint64_t)(a.K / 2), (cuuint64_t)a.N};
+    // 4-byte elements: a box row is 128 * SUB bytes, beyond the 256-element limit of a byte-typed map
+    const int box_bytes = 128 * sub_chunks(Mpad);
+    const cuuint64_t dims[2] = {(cuuint64_t)(a.K / 8), (cuuint64_t)a.N};
     const cuuint64_t strides[1] = {(cuuint64_t)(a.K / 2)};
-    const cuuint32_t box[2] = {(cuuint32_t)(kKc / 2), (cuuint32_t)kRows};
+    const cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 4), (cuuint32_t)kRows};
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode_fn()(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.W), dims, strides,
+    const CUresult r = encode_fn()(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(a.W), dims, strides,
                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
@@ -463,8 +568,8 @@ cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st) {
     t.nkb = a.K / 16;
     t.partial = reinterpret_cast<float*>(scratch + part_off);
     t.tickets = reinterpret_cast<unsigned int*>(scratch);
-    t.N = a.N; t.M = M; t.Mpad = Mpad; t.nchunks = nchunks; t.ksplit = ksplit;
-    const int grid = tiles * ksplit;
+    t.N = a.N; t.M = M; t.Mpad = Mpad; t.nchunks = nchunks; t.ksplit = ksplit; t.map_elem = 4; t.debug = g_tc_debug;
+    const int grid = tiles * ksplit < sms ? tiles * ksplit : sms;  // persistent: one CTA per SM at most
     if (Mpad == 16) return launch_n<16>(map_w, t, grid, st);
     if (Mpad == 32) return launch_n<32>(map_w, t, grid, st);
     return launch_n<64>(map_w, t, grid, st);

@@ -6,16 +6,18 @@
 // The scale changes every 16 k, the MMA consumes 32 k: each k-block gets its own MMA whose A operand holds the
 // block in its first 16-byte K core matrix and a shared all-zero core matrix in the second (the descriptor's
 // leading-dimension offset points the second K step at the zero region), so every accumulator tile is the exact
-// int32 dot product of ONE k-block.  Accumulator tiles start from the bit pattern of 1.5 * 2^23, so the value
-// read back is a float holding 12582912 + 16 * dot exactly and the per-block scaling is two FMAs per
-// (row, sequence, block): t = fma(F, w_sc, -12582912 * w_sc) (exact for binary16 scales), acc = fma(t, x_sc/16, acc).
+// int32 dot product of ONE k-block.  The epilogue adds the bit pattern of 1.5 * 2^23 to the integer it reads back,
+// which makes it a float holding 12582912 + 16 * dot exactly, and scales with two FMAs per (row, sequence,
+// block): t = fma(F, w_sc, -12582912 * w_sc) (exact for binary16 scales), acc = fma(t, x_sc/16, acc).
 //
-// Roles inside a CTA of 12 warps (one CTA works on 128 weight rows x a range of 256-k chunks):
+// Roles inside a persistent CTA of 12 warps (a work unit is 128 weight rows x a range of 256-k chunks):
 //   warp 0      producer: TMA 2-D loads of packed nibbles and weight scales, bulk copies of the activations
 //   warp 1      MMA issuer (one elected lane)
-//   warps 4-7   epilogue: tcgen05.ld, scaling, fp32 accumulation in registers, refill of the tile with the
-//               magic pattern, final store (thread = weight row = TMEM lane)
-//   warps 8-11  unpack: nibbles -> signed bytes 16*q in the K-major core-matrix layout the MMA reads
+//   warps 2-3   weight-scale loader: cp.async of each row's 16 scales per chunk into a ring, eight chunks ahead
+//   warps 4-11  epilogue: tcgen05.ld, scaling, fp32 accumulation in registers, final store (thread = weight row
+//               = TMEM lane; warps 4-7 take the first half of the sequences, warps 8-11 the second, so that
+//               every scheduler has two epilogue warps to overlap and each thread keeps half the accumulators)
+//   warps 12-15 unpack: nibbles -> signed bytes 16*q in the K-major core-matrix layout the MMA reads
 // All waits are bounded; a wait that gives up raises an abort flag that every role polls.
 #pragma once
 #include <cuda.h>
@@ -28,16 +30,17 @@ namespace tc {
 constexpr int kKc = 256;          // k per chunk = 16 k-blocks
 constexpr int kBlocksPerChunk = 16;
 constexpr int kRows = 128;        // weight rows per CTA tile = MMA M
-constexpr int kSP = 3;            // packed-nibble ring slots
+constexpr int kSP = 4;            // packed-nibble ring slots
 constexpr int kSA = 2;            // operand (A int8 + B) ring slots
 constexpr int kSS = 4;            // scale ring slots
+constexpr int kSW = 8;            // weight-scale ring slots (one chunk of one tile each)
 constexpr int kABlockStride = 2048 + 16;  // bytes between the int8 tiles of consecutive k-blocks (odd 16-byte count
                                           // spreads the unpack stores over the shared-memory banks)
 constexpr int kPackedBytes = kRows * (kKc / 2);                  // 16384
 constexpr int kWScaleBytes = kRows * kBlocksPerChunk * 2;        // 4096
 constexpr int kAStageBytes = kBlocksPerChunk * kABlockStride;    // 33024
 constexpr int kZeroBytes = 2048;
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;
 
 struct TcArgs {
     float* y;                 // [M][y_stride]
@@ -51,6 +54,8 @@ struct TcArgs {
     int N, M, Mpad;           // Mpad = MMA N in {16, 32, 64}
     int nchunks;              // ceil(K / 256)
     int ksplit;               // CTAs sharing one row tile
+    int debug;                // timing experiments (bit 1: no scaling, 2: no unpack, 4: no MMA, 8: no TMEM loads)
+    int map_elem;             // bytes per element of the weight tensor map (its x coordinate is in elements)
 };
 
 // bytes of one activation chunk in global memory: 16 blocks x Mpad rows x 16 B, then 16 x Mpad block scales
@@ -71,11 +76,13 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+// D = A * B (accumulate == 0) or D += A * B.
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(1u), "r"(0u)
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
@@ -85,6 +92,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(addr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(addr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_st16_const(uint32_t addr, uint32_t c) {
     asm volatile(
@@ -101,6 +114,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
+}
+// 4-byte asynchronous copy global -> shared; src_bytes 0 writes zeros.
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global.L2::256B [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// Makes the mbarrier receive one (pre-counted) arrival when all earlier cp.async of this thread have landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void bulk_g2s_plain(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

@@ -210,7 +210,7 @@ int bw_device_status(int* status_out);
 /* Tuning knobs for experiments: key 0 = ring stages (0 = automatic),
  * key 1 = CTAs per SM cap (0 = automatic), key 2 = force the plain-load kernel,
  * key 3 = rows per thread group and tile cap, key 4 = threads per CTA target,
- * key 5 = smallest batch sent to the tensor-core kernel (0 = default 9), key 6 = its K-split (0 = automatic). */
+ * key 5 = smallest batch sent to the tensor-core kernel (0 = default 8), key 6 = its K-split (0 = automatic). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);
