@@ -172,28 +172,46 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_split_kernel(cons
         __syncthreads();
         if (s_last) {
             __threadfence();
-#pragma unroll
-            for (int h = 0; h < GQ; ++h) {
-                mx[h] = -FLT_MAX; l[h] = 0.f; o[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-                const float* base = a.part + ((size_t)m * a.nqh + h0 + h) * a.nsplit * kPartStride;
-                for (int s = warp; s < a.nsplit; s += kAttnWarps) {
-                    const float* rec = base + (size_t)s * kPartStride;
-                    const float ls = __ldcg(rec + kHd + 1);
-                    if (ls > 0.f) {
-                        const float ms = __ldcg(rec + kHd);
-                        const float2 r0 = __ldcg(reinterpret_cast<const float2*>(rec + 4 * lane));
-                        const float2 r1 = __ldcg(reinterpret_cast<const float2*>(rec + 4 * lane + 2));
-                        const float mnew = fmaxf(mx[h], ms);
-                        const float c0 = __expf(mx[h] - mnew), c1 = __expf(ms - mnew);
-                        o[h] = make_float4(o[h].x * c0 + r0.x * c1, o[h].y * c0 + r0.y * c1, o[h].z * c0 + r1.x * c1,
-                                           o[h].w * c0 + r1.y * c1);
-                        l[h] = l[h] * c0 + ls * c1;
-                        mx[h] = mnew;
+            // One warp per head: lanes first run over the splits (maxima, weights, sum), then over the 128
+            // outputs, four each, with the split weights broadcast by shuffle; every record load is independent.
+            for (int h = warp; h < GQ; h += kAttnWarps) {
+                const size_t head = (size_t)m * a.nqh + h0 + h;
+                const float* base = a.part + head * a.nsplit * kPartStride;
+                float mloc = -FLT_MAX;
+                for (int s = lane; s < a.nsplit; s += 32)
+                    if (__ldcg(base + (size_t)s * kPartStride + kHd + 1) > 0.f)
+                        mloc = fmaxf(mloc, __ldcg(base + (size_t)s * kPartStride + kHd));
+                const float mall = warp_max(mloc);
+                float lsum = 0.f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s0 = 0; s0 < a.nsplit; s0 += 32) {
+                    const int s = s0 + lane;
+                    float c = 0.f;
+                    if (s < a.nsplit) {
+                        const float ls = __ldcg(base + (size_t)s * kPartStride + kHd + 1);
+                        if (ls > 0.f) {
+                            c = __expf(__ldcg(base + (size_t)s * kPartStride + kHd) - mall);
+                            lsum = fmaf(ls, c, lsum);
+                        }
+                    }
+                    const int cnt = min(32, a.nsplit - s0);
+#pragma unroll 4
+                    for (int j = 0; j < cnt; ++j) {
+                        const float cj = __shfl_sync(0xffffffffu, c, j);
+                        if (cj != 0.f) {
+                            const float* rec = base + (size_t)(s0 + j) * kPartStride + 4 * lane;
+                            const float2 r0 = __ldcg(reinterpret_cast<const float2*>(rec));
+                            const float2 r1 = __ldcg(reinterpret_cast<const float2*>(rec + 2));
+                            acc.x = fmaf(cj, r0.x, acc.x); acc.y = fmaf(cj, r0.y, acc.y);
+                            acc.z = fmaf(cj, r1.x, acc.z); acc.w = fmaf(cj, r1.y, acc.w);
+                        }
                     }
                 }
+                lsum = warp_sum(lsum);
+                const float inv = 1.0f / (lsum + 1e-9f);
+                *reinterpret_cast<float4*>(a.out + head * kHd + 4 * lane) =
+                    make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
             }
-            __syncthreads();
-            merge_warps_and_emit(true);
             if (t == 0) a.tickets[m * a.nkv + kvh] = 0;
         }
     }
