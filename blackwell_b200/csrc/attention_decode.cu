@@ -58,6 +58,8 @@ template <typename KVT, int GQ>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_split_kernel(const AttnArgs a) {
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    pdl_trigger();
+    pdl_wait();  // Q, the cache rows of this step and the positions come from the kernels before
     const int seq_pos = a.d_seq_pos ? a.d_seq_pos[a.per_seq ? m : 0] : a.seq_pos;
     const int npos = min(seq_pos + 1, a.max_seq);
     const int p0 = split * a.split_len;
@@ -311,14 +313,15 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
         a.part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(base) + tick_bytes);
     }
     const dim3 grid(nsplit, a.nkv, a.M);
+    cudaError_t le;
     switch (gq) {
-        case 1: attn_decode_split_kernel<KVT, 1><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
-        case 2: attn_decode_split_kernel<KVT, 2><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
-        case 4: attn_decode_split_kernel<KVT, 4><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
-        default: attn_decode_split_kernel<KVT, 8><<<grid, kAttnWarps * 32, 0, st>>>(a); break;
+        case 1: le = launch_pdl(attn_decode_split_kernel<KVT, 1>, grid, dim3(kAttnWarps * 32), 0, st, a); break;
+        case 2: le = launch_pdl(attn_decode_split_kernel<KVT, 2>, grid, dim3(kAttnWarps * 32), 0, st, a); break;
+        case 4: le = launch_pdl(attn_decode_split_kernel<KVT, 4>, grid, dim3(kAttnWarps * 32), 0, st, a); break;
+        default: le = launch_pdl(attn_decode_split_kernel<KVT, 8>, grid, dim3(kAttnWarps * 32), 0, st, a); break;
     }
     count_launch(1);
-    return cudaPeekAtLastError();
+    return le != cudaSuccess ? le : cudaPeekAtLastError();
 }
 
 }  // namespace bw

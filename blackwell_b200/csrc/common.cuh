@@ -62,6 +62,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
 }
 
+// ------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in the stream
+// is still running.  pdl_wait() blocks until the predecessor has completed and its writes are visible: everything
+// that reads the predecessor's output, or writes what it may still read, comes after it.  pdl_trigger() lets the
+// successor begin its own preamble.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // -------------------------------------------------------- bulk async copies
 // 1-D bulk copy global -> shared of this CTA, completion counted in bytes on an
 // mbarrier.  Both addresses 16-byte aligned, size a multiple of 16.  No cluster

@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_kernel(float* q_out, __ha
                                                               const float* k_norm_w, const int* d_seq_pos, int nqh,
                                                               int nkv, int max_seq, int M, size_t kv_batch_elems,
                                                               size_t kv_layer_elems, float eps, float rope_base) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int heads = nqh + 2 * nkv;
     const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -166,11 +168,12 @@ extern "C" int bw_qk_norm_rope_kv_f16(float* q_out, uint16_t* k_cache, uint16_t*
     if (head_dim != kHeadDim || num_q_heads < 1 || num_kv_heads < 1 || M < 1 || max_seq_len < 1)
         return cudaErrorInvalidValue;
     const int warps = M * (num_q_heads + 2 * num_kv_heads);
-    qk_norm_rope_kv_kernel<<<(warps + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        q_out, reinterpret_cast<__half*>(k_cache), reinterpret_cast<__half*>(v_cache), qkv, q_norm_w, k_norm_w,
-        d_seq_pos, num_q_heads, num_kv_heads, max_seq_len, M, kv_batch_elems, kv_layer_elems, eps, rope_base);
+    cudaError_t le = launch_pdl(qk_norm_rope_kv_kernel, dim3((warps + 3) / 4), dim3(128), 0,
+                                static_cast<cudaStream_t>(stream), q_out, reinterpret_cast<__half*>(k_cache),
+                                reinterpret_cast<__half*>(v_cache), qkv, q_norm_w, k_norm_w, d_seq_pos, num_q_heads,
+                                num_kv_heads, max_seq_len, M, kv_batch_elems, kv_layer_elems, eps, rope_base);
     count_launch(1);
-    return cudaPeekAtLastError();
+    return le != cudaSuccess ? le : cudaPeekAtLastError();
 }
 
 extern "C" int bw_embed_gather_f16(float* x_out, const uint16_t* table_f16, const int* d_tokens, int H, int vocab,

@@ -122,6 +122,8 @@ static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0},
 static std::atomic<long long> g_launches{0};
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+static std::atomic<int> g_pdl{1};
+bool pdl_enabled() { return g_pdl.load() != 0; }
 
 struct StreamPlan {
     bool ok = false;
@@ -162,9 +164,9 @@ static cudaError_t launch_stream_inst(const GemvArgs& a, const StreamPlan& p, cu
     const int units = p.n_rows / p.row_unit;
     int grid = sm_count(dev) * occ;
     if (grid > units) grid = units;
-    kern<<<grid, p.T, p.smem, st>>>(a);
+    cudaError_t le = launch_pdl(kern, dim3(grid), dim3(p.T), p.smem, st, a);
     count_launch(1);
-    return cudaPeekAtLastError();
+    return le != cudaSuccess ? le : cudaPeekAtLastError();
 }
 
 template <int M, typename WS>
@@ -436,6 +438,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 5: g_tune_tc_min = value; return 0;
         case 6: tc::set_ksplit_override(value); return 0;
         case 7: tc::set_debug(value); return 0;
+        case 8: g_pdl = value; return 0;
         default: return cudaErrorInvalidValue;
     }
 }

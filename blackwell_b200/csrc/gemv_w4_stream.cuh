@@ -329,6 +329,9 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         const int pre = min(S, ntiles);
         for (int i = 0; i < pre; ++i) issue_tile(i);
     }
+    // The weights never depend on the previous kernel, the activations and y do: only now wait for it.
+    pdl_trigger();
+    pdl_wait();
 
     // ---- activation prologue (overlaps the first weight tiles in flight) ----
     const bool needs_norm = (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4);
