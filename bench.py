@@ -167,6 +167,14 @@ def run_reference(args, rank):
         times.append(dt)
     mats = gemv_set()
     nbytes = sum(shapes.gemv_bytes(max(16, N // frac), K, 1, 2, "f16") for _, N, K in mats)
+    ref_gpu = None
+    try:  # beside the CPU number: the reference's own CUDA kernels on this GPU, when there is one
+        import torch
+
+        if torch.cuda.is_available():
+            ref_gpu = per_matrix_times(torch.device("cuda", 0), 1, reference_arm=True)
+    except Exception as exc:
+        ref_gpu = {"error": repr(exc)[:200]}
     t = float(np.mean(times))
     val = nbytes / t / 1e9
     line = {
@@ -178,6 +186,7 @@ def run_reference(args, rank):
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "reference_cuda_kernels_sm100a": ref_gpu,
     }
     print(json.dumps(line), flush=True)
 
@@ -303,24 +312,13 @@ def run_ours(args, rank, world, local_rank):
         e2e_sec = float(tmax.item())
     e2e_val = total_bytes / e2e_sec / 1e9
 
-    # ---- per-matrix launch durations (CUDA events around each launch, same stream), L2 flushed by the
-    # other matrices of the set between two launches of the same matrix
+    # ---- every matrix on its own, L2-cold, beside the reference's own CUDA kernel (rank 0, single GPU)
     per = []
-    if rank == 0:
-        evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in state]
-               for _ in range(10)]
-        for rep in evs:
-            for (a, b), (sh, W, sc, x, y) in zip(rep, state):
-                a.record()
-                k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
-                b.record()
-        torch.cuda.synchronize()
-        peak, _ = measured_peak()
-        for i, (sh, *_rest) in enumerate(state):
-            us = float(np.median([rep[i][0].elapsed_time(rep[i][1]) for rep in evs])) * 1e3
-            b = shapes.gemv_bytes(sh.n_local, sh.k_local, M, 2, "f16")
-            per.append({"name": sh.name, "N": sh.n_local, "K": sh.k_local, "us": round(us, 2),
-                        "gbs": round(b / us / 1e3, 1), "frac": round(b / us / 1e3 / peak, 3)})
+    if rank == 0 and world == 1 and not args.only:
+        try:
+            per = per_matrix_times(dev, M)
+        except Exception as exc:
+            per = [{"error": repr(exc)[:200]}]
     if world > 1:
         barrier()
 
@@ -365,6 +363,82 @@ def run_ours(args, rank, world, local_rank):
         "decode": decode,
     }
     print(json.dumps(line), flush=True)
+
+
+def _graph_us(run, reps):
+    """Median-of-3 time per call of run(i), i = 0..reps-1 captured in one CUDA graph."""
+    import torch
+
+    for i in range(min(reps, 3)):
+        run(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(reps):
+            run(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ts = []
+    for _ in range(3):
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / reps * 1e3)
+    return float(np.median(ts))
+
+
+def per_matrix_times(dev, M, reference_arm=False):
+    """Each matrix of the set on its own, L2-cold: a CUDA graph of 24 launches rotating over enough distinct
+    weight copies to exceed twice the L2.  Our arm times the W4A8 kernel (fused f16 quantize) and our kernels in the
+    reference's own format (quantize_int4 + gemv_int4_batched, W4A4, fp32 scales, LM head rows padded to a
+    multiple of 16 as the reference requires).  The reference arm times the reference's own CUDA kernels, rebuilt
+    unchanged for sm_100a (oracle/_ref), on the same shapes in that format: the GPU kernel to beat."""
+    import torch
+
+    from blackwell_b200 import synth
+    have_ref = False
+    if reference_arm:
+        from oracle import ref_cuda
+
+        have_ref = ref_cuda.available()
+        if not have_ref:
+            return None
+    else:
+        from blackwell_b200 import kernels as k
+    peak, _ = measured_peak()
+    out = []
+    for i, (name, N, K) in enumerate(gemv_set()):
+        Np = (N + 15) // 16 * 16
+        ncopy = int(min(24, max(2, 300e6 // (Np * K * 0.5625) + 1)))
+        Ws = [synth.int4_weights_device(Np, K, 700 + 31 * i + c, device=dev) for c in range(ncopy)]
+        x16 = synth.activations_f16_device(M, K, 701 + i, device=dev)
+        y = torch.empty((M, Np), dtype=torch.float32, device=dev)
+        rec = {"name": name, "N": N, "K": K}
+        if not reference_arm:
+            us = _graph_us(lambda j: k.gemv_w4a8_f16in(y, x16, Ws[j % ncopy][0], Ws[j % ncopy][1], K, N, M), 24)
+            b = shapes.gemv_bytes(N, K, M, 2, "f16")
+            rec.update({"us": round(us, 2), "gbs": round(b / us / 1e3, 1), "frac": round(b / us / 1e3 / peak, 3)})
+        if M <= 16:
+            sc32 = [w[1].float() for w in Ws]
+            x32 = x16.float()
+            q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+            s_ = torch.empty((M, K // 16), dtype=torch.float32, device=dev)
+            lib = ref_cuda if reference_arm else k
+
+            def chain(j):
+                lib.quantize_int4_batched(q, s_, x32, K, M)
+                lib.gemv_int4_batched(y, q, s_, Ws[j % ncopy][0], sc32[j % ncopy], K, Np, M)
+
+            b4 = shapes.gemv_bytes(Np, K, M, 4, "i4")
+            u = _graph_us(chain, 24)
+            rec["w4a4_fp32scale"] = {"rows": Np, "us": round(u, 2), "gbs": round(b4 / u / 1e3, 1)}
+            del sc32
+        out.append(rec)
+        del Ws
+        torch.cuda.empty_cache()
+    return out
 
 
 def run_decode(shape, batch, ctx, steps, dev, world=1, rank=0, max_seq=None):
