@@ -331,6 +331,12 @@ def run_ours(args, rank, world, local_rank):
                 decode.append(run_decode(shapes.QWEN3_8B, b, 2048, 20, dev, world, rank))
             except Exception as exc:  # the headline must survive a failure of the side measurement
                 decode.append({"model": shapes.QWEN3_8B.name, "batch": b, "error": repr(exc)[:200]})
+        if not args.no_decode32:
+            # configs[4]: Qwen3-32B-shape, batch 64, context 4096, tensor-parallel over all ranks
+            try:
+                decode.append(run_decode(shapes.QWEN3_32B, 64, 4096, 5, dev, world, rank))
+            except Exception as exc:
+                decode.append({"model": shapes.QWEN3_32B.name, "batch": 64, "error": repr(exc)[:200]})
     if rank != 0:
         return
     peak, peak_kind = measured_peak()
@@ -505,6 +511,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying "
                     "a captured CUDA graph")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode-step side measurement")
+    ap.add_argument("--no-decode32", action="store_true", help="skip the 32B-shape decode side measurement")
     ap.add_argument("--decode-only", default=None, help="profiling aid: only the decode step, MODEL:BATCH:CTX "
                     "(MODEL = 8b or 32b); prints its own JSON line")
     ap.add_argument("--batch", type=int, default=1, help="profiling aid: sequences per GEMV (the headline is 1)")

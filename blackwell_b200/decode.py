@@ -99,10 +99,11 @@ class DecodeEngine:
         g.manual_seed(synth.SEED_BASE + seed + self.rank)
         for c in (self.kc, self.vc):
             v = c.view(self.M, self.s.layers, self.nkv, self.max_seq, 128)
-            tmp = torch.empty((self.M, self.s.layers, self.nkv, ctx, 128), dtype=torch.float32, device=self.dev)
-            tmp.normal_(0.0, 1.0, generator=g)
-            v[:, :, :, :ctx].copy_(tmp)
-            del tmp
+            for l in range(self.s.layers):  # layer by layer: the fp32 staging buffer stays small
+                tmp = torch.empty((self.M, self.nkv, ctx, 128), dtype=torch.float32, device=self.dev)
+                tmp.normal_(0.0, 1.0, generator=g)
+                v[:, l, :, :ctx].copy_(tmp)
+                del tmp
         self.pos.fill_(ctx - 1)
         self.ctx_hint = min(self.max_seq, ctx + 64)
 
