@@ -18,6 +18,7 @@
 #include <mutex>
 
 #include "../../include/blackwell_b200.h"
+#include "attention_mma.cuh"
 #include "common.cuh"
 #include "host_util.h"
 
@@ -219,6 +220,116 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_split_kernel(cons
     }
 }
 
+// Tensor-core variant for the binary16 cache (see attention_mma.cuh): same grid, same splits, same partial records
+// and arrival counters as the scalar kernel above.
+template <int GQ>
+__global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const AttnArgs a) {
+    const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    pdl_trigger();
+    pdl_wait();
+    const int seq_pos = a.d_seq_pos ? a.d_seq_pos[a.per_seq ? m : 0] : a.seq_pos;
+    const int npos = min(seq_pos + 1, a.max_seq);
+    const int p0 = split * a.split_len;
+    const int p1 = min(npos, p0 + a.split_len);
+    const __half* Kb = static_cast<const __half*>(a.K) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
+                       (size_t)kvh * a.max_seq * kHd;
+    const __half* Vb = static_cast<const __half*>(a.V) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
+                       (size_t)kvh * a.max_seq * kHd;
+    const int h0 = kvh * GQ;
+
+    extern __shared__ __align__(128) unsigned char attn_dsm[];   // 4 warps x (K, V) x 2 buffers x 4 KB
+    __shared__ __align__(16) float s_q[GQ][kHd];
+    __shared__ float s_m[kAttnWarps][GQ], s_l[kAttnWarps][GQ];
+    __shared__ float s_o[kAttnWarps][GQ][kHd];
+    __shared__ int s_last;
+    for (int i = t; i < GQ * kHd; i += blockDim.x) s_q[i / kHd][i % kHd] = a.Q[((size_t)m * a.nqh + h0) * kHd + i];
+    __syncthreads();
+
+    float m_run, l_run, o[32];
+    amma::warp_stream<GQ>(Kb, Vb, &s_q[0][0], a.scale, p0, p1, warp, kAttnWarps, attn_dsm + warp * amma::kWarpSmem,
+                          m_run, l_run, o);
+    {
+        const int g = lane >> 2, tq = lane & 3;
+        if (g < GQ) {
+            if (tq == 0) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
+#pragma unroll
+            for (int jn = 0; jn < 16; ++jn)
+                *reinterpret_cast<float2*>(&s_o[warp][g][8 * jn + 2 * tq]) = make_float2(o[2 * jn], o[2 * jn + 1]);
+        }
+    }
+    __syncthreads();
+    for (int idx = t; idx < GQ * kHd; idx += blockDim.x) {
+        const int h = idx / kHd, d = idx - h * kHd;
+        float mm = -FLT_MAX;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, s_m[w][h]);
+        float ls = 0.f, os = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float c = __expf(s_m[w][h] - mm);
+            ls = fmaf(s_l[w][h], c, ls);
+            os = fmaf(s_o[w][h][d], c, os);
+        }
+        const size_t head = (size_t)m * a.nqh + h0 + h;
+        if (a.nsplit == 1) {
+            a.out[head * kHd + d] = os * (1.0f / (ls + 1e-9f));
+        } else {
+            float* rec = a.part + (head * a.nsplit + split) * kPartStride;
+            rec[d] = os;
+            if (d == 0) { rec[kHd] = mm; rec[kHd + 1] = ls; }
+        }
+    }
+    if (a.nsplit > 1 && a.tickets) {
+        __threadfence();
+        __syncthreads();
+        if (t == 0) s_last = (atomicAdd(&a.tickets[m * a.nkv + kvh], 1u) == (unsigned)a.nsplit - 1) ? 1 : 0;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            for (int h = warp; h < GQ; h += kAttnWarps) {
+                const size_t head = (size_t)m * a.nqh + h0 + h;
+                const float* base = a.part + head * a.nsplit * kPartStride;
+                float mloc = -FLT_MAX;
+                for (int s = lane; s < a.nsplit; s += 32)
+                    if (__ldcg(base + (size_t)s * kPartStride + kHd + 1) > 0.f)
+                        mloc = fmaxf(mloc, __ldcg(base + (size_t)s * kPartStride + kHd));
+                const float mall = warp_max(mloc);
+                float lsum = 0.f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s0 = 0; s0 < a.nsplit; s0 += 32) {
+                    const int s = s0 + lane;
+                    float c = 0.f;
+                    if (s < a.nsplit) {
+                        const float ls = __ldcg(base + (size_t)s * kPartStride + kHd + 1);
+                        if (ls > 0.f) {
+                            c = __expf(__ldcg(base + (size_t)s * kPartStride + kHd) - mall);
+                            lsum = fmaf(ls, c, lsum);
+                        }
+                    }
+                    const int cnt = min(32, a.nsplit - s0);
+#pragma unroll 4
+                    for (int j = 0; j < cnt; ++j) {
+                        const float cj = __shfl_sync(0xffffffffu, c, j);
+                        if (cj != 0.f) {
+                            const float* rec = base + (size_t)(s0 + j) * kPartStride + 4 * lane;
+                            const float2 r0 = __ldcg(reinterpret_cast<const float2*>(rec));
+                            const float2 r1 = __ldcg(reinterpret_cast<const float2*>(rec + 2));
+                            acc.x = fmaf(cj, r0.x, acc.x); acc.y = fmaf(cj, r0.y, acc.y);
+                            acc.z = fmaf(cj, r1.x, acc.z); acc.w = fmaf(cj, r1.y, acc.w);
+                        }
+                    }
+                }
+                lsum = warp_sum(lsum);
+                const float inv = 1.0f / (lsum + 1e-9f);
+                *reinterpret_cast<float4*>(a.out + head * kHd + 4 * lane) =
+                    make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            }
+            if (t == 0) a.tickets[m * a.nkv + kvh] = 0;
+        }
+    }
+}
+
 // Merges the per-split partial records of one (sequence, head).
 __global__ void __launch_bounds__(kHd) attn_merge_kernel(float* out, const float* part, int nsplit) {
     const size_t head = blockIdx.x;
@@ -259,6 +370,8 @@ struct Scratch {
     size_t bytes = 0;
 };
 static Scratch g_scratch[kMaxDevices];
+static int g_attn_mma = 1;  // 0: keep the scalar kernel for the binary16 cache too (comparison runs)
+void set_attn_mma(int v) { g_attn_mma = v; }
 static std::mutex g_scratch_mu;
 
 // Grow-only per-device scratch for the split partials.  Growing frees and
@@ -314,6 +427,19 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     }
     const dim3 grid(nsplit, a.nkv, a.M);
     cudaError_t le;
+    if (sizeof(KVT) == 2 && (gq == 4 || gq == 8) && g_attn_mma) {
+        // binary16 cache with grouped heads: the tensor-core kernel
+        const size_t dsm = (size_t)kAttnWarps * amma::kWarpSmem;
+        static std::once_flag once[kMaxDevices];
+        std::call_once(once[current_device()], [&] {
+            cudaFuncSetAttribute(attn_decode_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm);
+            cudaFuncSetAttribute(attn_decode_mma_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsm);
+        });
+        le = gq == 4 ? launch_pdl(attn_decode_mma_kernel<4>, grid, dim3(kAttnWarps * 32), dsm, st, a)
+                     : launch_pdl(attn_decode_mma_kernel<8>, grid, dim3(kAttnWarps * 32), dsm, st, a);
+        count_launch(1);
+        return le != cudaSuccess ? le : cudaPeekAtLastError();
+    }
     switch (gq) {
         case 1: le = launch_pdl(attn_decode_split_kernel<KVT, 1>, grid, dim3(kAttnWarps * 32), 0, st, a); break;
         case 2: le = launch_pdl(attn_decode_split_kernel<KVT, 2>, grid, dim3(kAttnWarps * 32), 0, st, a); break;

@@ -13,6 +13,8 @@
 
 namespace bw {
 
+void set_attn_mma(int v);  // attention_decode.cu
+
 namespace tc {  // tensor-core path, gemm_w4a8_tc.cu
 bool eligible(const GemvArgs& a, int M);
 cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st);
@@ -439,6 +441,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 6: tc::set_ksplit_override(value); return 0;
         case 7: tc::set_debug(value); return 0;
         case 8: g_pdl = value; return 0;
+        case 9: set_attn_mma(value); return 0;
         default: return cudaErrorInvalidValue;
     }
 }
