@@ -155,6 +155,15 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_ptr;
+    if (warp >= 4 && warp < 8) {
+        // every accumulator column of this thread's lane starts at the magic pattern
+        const uint32_t la = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        for (int c = 0; c < 512; c += 16) tmem_st16_const(la + c, (uint32_t)kMagicInt);
+        tmem_wait_st();
+        tc_fence_before();
+    }
+    __syncthreads();
+    tc_fence_after();
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ producer
@@ -226,7 +235,7 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                             // B: first K step = the block; the second multiplies zeros, any valid rows will do
                             const uint32_t b_addr = b_base + b * NMMA * 16;
                             const uint64_t db = smem_desc(b_addr, b == kBlocksPerChunk - 1 ? 0 : NMMA * 16, 128);
-                            tc_mma_i8(tmem + dg * 256 + bi * NMMA, da, db, idesc, 0u);
+                            tc_mma_i8(tmem + dg * 256 + bi * NMMA, da, db, idesc, 1u);
                         }
                         tc_commit(bar(kDFull + dg));
                     }
@@ -343,12 +352,13 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                     if (!wait(kDFull + dg, (gcount >> 1) & 1)) { ok = false; break; }
                     ++gcount;
                     tc_fence_after();
-                    // blocks of the group in pairs: two loads in flight per wait
+                    // PB blocks of the group per wait (at least 32 accumulator words in flight, within the register budget)
+                    constexpr int PB = CW >= 32 ? 1 : 2;
 #pragma unroll
-                    for (int bi = 0; bi < GB; bi += 2) {
-                        uint32_t v[2][CW];
+                    for (int bi = 0; bi < GB; bi += PB) {
+                        uint32_t v[PB][CW];
 #pragma unroll
-                        for (int p = 0; p < 2; ++p) {
+                        for (int p = 0; p < PB; ++p) {
                             if (a.debug & 8) break;
                             const uint32_t addr = lane_addr + dg * 256 + (bi + p) * NMMA;
                             if constexpr (CW == 8) {
@@ -360,13 +370,25 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                             }
                         }
                         tmem_wait_ld();
-                        if (bi == GB - 2) {  // the whole group is in registers: the MMA warp may overwrite it
+                        // hand the columns back holding the magic pattern
+#pragma unroll
+                        for (int p = 0; p < PB; ++p) {
+                            const uint32_t addr = lane_addr + dg * 256 + (bi + p) * NMMA;
+                            if constexpr (CW == 8) {
+                                tmem_st8_const(addr, (uint32_t)kMagicInt);
+                            } else {
+#pragma unroll
+                                for (int c = 0; c < CW; c += 16) tmem_st16_const(addr + c, (uint32_t)kMagicInt);
+                            }
+                        }
+                        if (bi == GB - PB) {  // the whole group is in registers and refilled: the MMA warp may go on
+                            tmem_wait_st();
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(bar(kDEmpty + dg));
                         }
 #pragma unroll
-                        for (int p = 0; p < 2; ++p) {
+                        for (int p = 0; p < PB; ++p) {
                             if (a.debug & 1) break;
                             const int b = g * GB + bi + p;              // k-block within the chunk
                             const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&wcur[b >> 1]));
@@ -375,14 +397,11 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
 #pragma unroll
                             for (int q = 0; q < CW / 4; ++q) {
                                 const float4 s4 = *reinterpret_cast<const float4*>(sx + b * NMMA + 4 * q);
-                                const float f0 = __int_as_float((int)v[p][4 * q + 0] + kMagicInt);
-                                const float f1 = __int_as_float((int)v[p][4 * q + 1] + kMagicInt);
-                                const float f2 = __int_as_float((int)v[p][4 * q + 2] + kMagicInt);
-                                const float f3 = __int_as_float((int)v[p][4 * q + 3] + kMagicInt);
-                                acc[4 * q + 0] = fmaf(fmaf(f0, w, cn), s4.x, acc[4 * q + 0]);
-                                acc[4 * q + 1] = fmaf(fmaf(f1, w, cn), s4.y, acc[4 * q + 1]);
-                                acc[4 * q + 2] = fmaf(fmaf(f2, w, cn), s4.z, acc[4 * q + 2]);
-                                acc[4 * q + 3] = fmaf(fmaf(f3, w, cn), s4.w, acc[4 * q + 3]);
+                                float t0, t1, t2, t3;
+                                ffma2(t0, t1, __uint_as_float(v[p][4 * q + 0]), __uint_as_float(v[p][4 * q + 1]), w, w, cn, cn);
+                                ffma2(t2, t3, __uint_as_float(v[p][4 * q + 2]), __uint_as_float(v[p][4 * q + 3]), w, w, cn, cn);
+                                ffma2(acc[4 * q + 0], acc[4 * q + 1], t0, t1, s4.x, s4.y, acc[4 * q + 0], acc[4 * q + 1]);
+                                ffma2(acc[4 * q + 2], acc[4 * q + 3], t2, t3, s4.z, s4.w, acc[4 * q + 2], acc[4 * q + 3]);
                             }
                         }
                     }

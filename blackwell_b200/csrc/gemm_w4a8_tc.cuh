@@ -6,9 +6,10 @@
 // The scale changes every 16 k, the MMA consumes 32 k: each k-block gets its own MMA whose A operand holds the
 // block in its first 16-byte K core matrix and a shared all-zero core matrix in the second (the descriptor's
 // leading-dimension offset points the second K step at the zero region), so every accumulator tile is the exact
-// int32 dot product of ONE k-block.  The epilogue adds the bit pattern of 1.5 * 2^23 to the integer it reads back,
-// which makes it a float holding 12582912 + 16 * dot exactly, and scales with two FMAs per (row, sequence,
-// block): t = fma(F, w_sc, -12582912 * w_sc) (exact for binary16 scales), acc = fma(t, x_sc/16, acc).
+// int32 dot product of ONE k-block.  Accumulator tiles start from the bit pattern of 1.5 * 2^23 (the epilogue stores
+// it back after every read), so the value read is a float holding 12582912 + 16 * dot exactly and the per-block
+// scaling is two FMAs per (row, sequence, block): t = fma(F, w_sc, -12582912 * w_sc) (exact for binary16
+// scales), acc = fma(t, x_sc/16, acc) -- issued as packed fp32x2 instructions, two sequences at a time.
 //
 // Roles inside a persistent CTA of 12 warps (a work unit is 128 weight rows x a range of 256-k chunks):
 //   warp 0      producer: TMA 2-D loads of packed nibbles and weight scales, bulk copies of the activations
@@ -99,11 +100,23 @@ __device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&v)[8]) {
                  : "r"(addr)
                  : "memory");
 }
+__device__ __forceinline__ void tmem_st8_const(uint32_t addr, uint32_t c) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(addr), "r"(c) : "memory");
+}
 __device__ __forceinline__ void tmem_st16_const(uint32_t addr, uint32_t c) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
         ::"r"(addr), "r"(c)
         : "memory");
+}
+// Two fp32 FMAs in one instruction (sm_100 packed single precision): d = a * b + c lane-wise on register pairs.
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    unsigned long long A, B, C, D;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(A) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(B) : "f"(b0), "f"(b1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(C) : "f"(c0), "f"(c1));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(D) : "l"(A), "l"(B), "l"(C));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(D));
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
