@@ -502,6 +502,44 @@ def run_decode(shape, batch, ctx, steps, dev, world=1, rank=0, max_seq=None):
     return out
 
 
+def run_attention_only(args):
+    """The fp16-KV decode attention kernel alone on a synthetic cache (one layer, every sequence at position CTX - 1):
+    the timed loop launches it args.steps times from the host; bytes = the K and V rows read."""
+    import torch
+
+    from blackwell_b200 import kernels as k
+
+    b, ctx, nqh, nkv = (int(v) for v in args.attn_only.split(":"))
+    hd = 128
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if args.tune:
+        for kv in args.tune.split(","):
+            key, _, val = kv.partition("=")
+            k.set_tuning(int(key), int(val))
+    g = torch.Generator(device="cuda").manual_seed(0xB2000005)
+    kv_batch = nkv * ctx * hd
+    kc = torch.randn((b, kv_batch), generator=g, device=dev, dtype=torch.float16)
+    vc = torch.randn((b, kv_batch), generator=g, device=dev, dtype=torch.float16)
+    q = torch.randn((b, nqh * hd), generator=g, device=dev, dtype=torch.float32)
+    out = torch.empty_like(q)
+    pos = torch.full((b,), ctx - 1, device=dev, dtype=torch.int32)
+    launch = lambda: k.attention_decode_f16kv(out, q, kc, vc, pos, ctx, nqh, nkv, hd, ctx, b, kv_batch, 0)
+    for _ in range(max(args.warmup, 1)):
+        launch()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / args.steps * 1e3
+    nbytes = 2 * b * kv_batch * 2
+    return {"kernel": "attention_decode_f16kv", "batch": b, "ctx": ctx, "q_heads": nqh, "kv_heads": nkv,
+            "us_per_launch": us, "kv_bytes": nbytes, "gbs": nbytes / us / 1e3, "device_status": k.device_status()}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -516,6 +554,8 @@ def main():
                     "(MODEL = 8b or 32b); prints its own JSON line")
     ap.add_argument("--batch", type=int, default=1, help="profiling aid: sequences per GEMV (the headline is 1)")
     ap.add_argument("--only", default=None, help="profiling aid: run one matrix of the set, NAME or NAME:ROWS")
+    ap.add_argument("--attn-only", default=None, help="profiling aid: only the fp16-KV GQA decode attention kernel, "
+                    "BATCH:CTX:NQH:NKV on a synthetic cache; prints its own JSON line")
     ap.add_argument("--tune", default=None, help="profiling aid: comma list of key=value for bw_set_tuning")
     args = ap.parse_args()
     global _ONLY
@@ -527,6 +567,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.attn_only:
+        print(json.dumps(run_attention_only(args)), flush=True)
         return
     if args.decode_only:
         import torch

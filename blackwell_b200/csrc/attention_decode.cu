@@ -241,8 +241,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const 
     extern __shared__ __align__(128) unsigned char attn_dsm[];   // 4 warps x (K, V) x 2 buffers x 4 KB
     __shared__ __align__(16) float s_q[GQ][kHd];
     __shared__ float s_m[kAttnWarps][GQ], s_l[kAttnWarps][GQ];
-    __shared__ float s_o[kAttnWarps][GQ][kHd];
     __shared__ int s_last;
+    // The per-warp results reuse the warp's own K/V staging area once its stream has drained.
+    auto s_o = [&](int w, int h) { return reinterpret_cast<float*>(attn_dsm + w * amma::kWarpSmem) + h * kHd; };
     for (int i = t; i < GQ * kHd; i += blockDim.x) s_q[i / kHd][i % kHd] = a.Q[((size_t)m * a.nqh + h0) * kHd + i];
     __syncthreads();
 
@@ -255,7 +256,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const 
             if (tq == 0) { s_m[warp][g] = m_run; s_l[warp][g] = l_run; }
 #pragma unroll
             for (int jn = 0; jn < 16; ++jn)
-                *reinterpret_cast<float2*>(&s_o[warp][g][8 * jn + 2 * tq]) = make_float2(o[2 * jn], o[2 * jn + 1]);
+                *reinterpret_cast<float2*>(s_o(warp, g) + 8 * jn + 2 * tq) = make_float2(o[2 * jn], o[2 * jn + 1]);
         }
     }
     __syncthreads();
@@ -269,7 +270,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const 
         for (int w = 0; w < kAttnWarps; ++w) {
             const float c = __expf(s_m[w][h] - mm);
             ls = fmaf(s_l[w][h], c, ls);
-            os = fmaf(s_o[w][h][d], c, os);
+            os = fmaf(s_o(w, h)[d], c, os);
         }
         const size_t head = (size_t)m * a.nqh + h0 + h;
         if (a.nsplit == 1) {
@@ -394,6 +395,28 @@ static cudaError_t attn_scratch(size_t bytes, float** out) {
     return cudaSuccess;
 }
 
+// Number of context splits: the grid is (sequence, kv head) pairs x splits, `slots` CTAs are resident at a time, and a
+// last wave that is mostly empty costs as much as a full one.  Takes the smallest split count (at least ~2 CTAs per SM, at least
+// 64 positions per split, at most 64 splits) whose last wave is at least 90 % full, else the fullest one.
+static int choose_splits(int pairs, int ctx, int slots) {
+    int max_split = (ctx + 63) / 64;
+    if (max_split > 64) max_split = 64;
+    if (max_split < 1) max_split = 1;
+    int lo = (slots + pairs - 1) / pairs;
+    if (lo > max_split) lo = max_split;
+    if (lo < 1) lo = 1;
+    int best = lo;
+    double best_eff = 0.0;
+    for (int n = lo; n <= max_split && n <= lo + 16; ++n) {
+        const long ctas = (long)pairs * n;
+        const long waves = (ctas + slots - 1) / slots;
+        const double eff = (double)ctas / (double)(waves * slots);
+        if (eff >= 0.9) return n;
+        if (eff > best_eff) { best_eff = eff; best = n; }
+    }
+    return best;
+}
+
 template <typename KVT>
 static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     if (!a.out || !a.Q || !a.K || !a.V || a.nqh < 1 || a.nkv < 1 || a.nqh % a.nkv != 0 || a.M < 1 || a.max_seq < 1)
@@ -402,13 +425,8 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return cudaErrorInvalidValue;
     if (ctx_hint < 1) ctx_hint = 1;
     if (ctx_hint > a.max_seq) ctx_hint = a.max_seq;
-    // enough CTAs for ~2 per SM, at least 64 positions per split
-    const int sms = sm_count(current_device());
-    int nsplit = (2 * sms + a.M * a.nkv - 1) / (a.M * a.nkv);
-    const int max_split = (ctx_hint + 63) / 64;
-    if (nsplit > max_split) nsplit = max_split;
-    if (nsplit > 64) nsplit = 64;
-    if (nsplit < 1) nsplit = 1;
+    const bool use_mma = sizeof(KVT) == 2 && (gq == 4 || gq == 8) && g_attn_mma;  // binary16 cache with grouped heads
+    int nsplit = choose_splits(a.M * a.nkv, ctx_hint, 2 * sm_count(current_device()));
     a.split_len = (ctx_hint + nsplit - 1) / nsplit;
     a.split_len = (a.split_len + kPosPerStep - 1) / kPosPerStep * kPosPerStep;
     nsplit = (ctx_hint + a.split_len - 1) / a.split_len;
@@ -427,8 +445,7 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     }
     const dim3 grid(nsplit, a.nkv, a.M);
     cudaError_t le;
-    if (sizeof(KVT) == 2 && (gq == 4 || gq == 8) && g_attn_mma) {
-        // binary16 cache with grouped heads: the tensor-core kernel
+    if (use_mma) {  // the tensor-core kernel
         const size_t dsm = (size_t)kAttnWarps * amma::kWarpSmem;
         static std::once_flag once[kMaxDevices];
         std::call_once(once[current_device()], [&] {

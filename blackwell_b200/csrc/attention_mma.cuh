@@ -111,17 +111,21 @@ __device__ __forceinline__ void warp_stream(const __half* Kb, const __half* Vb, 
         const int tpos = p0 + ti * kTile;
 
         // ---- S = Q K^T for 16 positions: s0/s1 = positions 2t, 2t+1 ; s4/s5 = positions 8 + 2t, 8 + 2t + 1
+        // four independent accumulator chains (high and low part of Q, two position tiles): a chain of dependent
+        // MMAs runs at one MMA per MMA latency, so the shorter the chains the better the tensor pipe is fed
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, s4 = 0.f, s5 = 0.f, s6 = 0.f, s7 = 0.f;
+        float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f, r4 = 0.f, r5 = 0.f, r6 = 0.f, r7 = 0.f;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             uint32_t b0, b1, b2, b3;
             const int mi = lane >> 3, rr = lane & 7;
             ldmatrix_x4(kt + tile_off((mi >> 1) * 8 + rr, 2 * ks + (mi & 1)), b0, b1, b2, b3);
             mma_16816(s0, s1, s2, s3, qh0[ks], qh2[ks], b0, b1);
-            mma_16816(s0, s1, s2, s3, ql0[ks], ql2[ks], b0, b1);
+            mma_16816(r0, r1, r2, r3, ql0[ks], ql2[ks], b0, b1);
             mma_16816(s4, s5, s6, s7, qh0[ks], qh2[ks], b2, b3);
-            mma_16816(s4, s5, s6, s7, ql0[ks], ql2[ks], b2, b3);
+            mma_16816(r4, r5, r6, r7, ql0[ks], ql2[ks], b2, b3);
         }
+        s0 += r0; s1 += r1; s4 += r4; s5 += r5;
         // ---- online softmax for head g over the 16 positions (4 per thread, 4 threads per head)
         const int pa = tpos + 2 * t, pb = tpos + 8 + 2 * t;
         s0 = pa < p1 ? s0 : -FLT_MAX;
