@@ -215,13 +215,22 @@ def run_ours(args, rank, world, local_rank):
         W, sc = synth.int4_weights_device(sh.n_local, sh.k_local, 500 + 17 * i + rank, device=dev)
         x = synth.activations_f16_device(M, sh.k_local, 600 + i, device=dev)
         y = torch.empty((M, sh.n_local), dtype=torch.float32, device=dev)
-        state.append((sh, W, sc, x, y))
-    coll = tp.Collectives(world, rank, dev) if world > 1 else None
+        state.append([sh, W, sc, x, y])
+    # Exchanges for N > 1: the K-split matrices (o, down) sum their partial results across ranks -- through the
+    # library's NVLink peer-load all-reduce by default, through NCCL with --exchange nccl; the row-split outputs
+    # (qkv, gate_up, lm_head) stay sharded, as their consumers in the decode step read them sharded.
+    coll = None
+    if world > 1:
+        coll = tp.Collectives(world, rank, dev, exchange=args.exchange, slot_floats=M * max(sh.N for sh in plan))
+        for st in state:
+            buf = coll.partial_buffer(st[0], M)
+            if buf is not None:
+                st[4] = buf
 
     def step():
         for sh, W, sc, x, y in state:
             k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
-            if coll is not None:
+            if coll is not None and sh.kind == "k":
                 coll.finish(sh, y)
 
     def barrier():
@@ -282,8 +291,8 @@ def run_ours(args, rank, world, local_rank):
         for hx, hy, (sh, W, sc, x, y) in zip(host_x, host_y, state):
             x.copy_(hx, non_blocking=True)
             k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
-            if coll is not None:
-                coll.finish(sh, y)
+            if coll is not None and sh.kind == "k":
+                y = coll.finish(sh, y)
             hy.copy_(y, non_blocking=True)
 
     if use_graph:
@@ -328,13 +337,13 @@ def run_ours(args, rank, world, local_rank):
     if not args.only and not args.no_decode:
         for b in (1, 8):
             try:
-                decode.append(run_decode(shapes.QWEN3_8B, b, 2048, 20, dev, world, rank))
+                decode.append(run_decode(shapes.QWEN3_8B, b, 2048, 20, dev, world, rank, exchange=args.exchange))
             except Exception as exc:  # the headline must survive a failure of the side measurement
                 decode.append({"model": shapes.QWEN3_8B.name, "batch": b, "error": repr(exc)[:200]})
         if not args.no_decode32:
             # configs[4]: Qwen3-32B-shape, batch 64, context 4096, tensor-parallel over all ranks
             try:
-                decode.append(run_decode(shapes.QWEN3_32B, 64, 4096, 5, dev, world, rank))
+                decode.append(run_decode(shapes.QWEN3_32B, 64, 4096, 5, dev, world, rank, exchange=args.exchange))
             except Exception as exc:
                 decode.append({"model": shapes.QWEN3_32B.name, "batch": 64, "error": repr(exc)[:200]})
     if rank != 0:
@@ -447,7 +456,7 @@ def per_matrix_times(dev, M, reference_arm=False):
     return out
 
 
-def run_decode(shape, batch, ctx, steps, dev, world=1, rank=0, max_seq=None):
+def run_decode(shape, batch, ctx, steps, dev, world=1, rank=0, max_seq=None, exchange="peer"):
     """Times the synthetic decode step (one CUDA graph per step) with the cache pre-filled to ``ctx``; returns a
     dict with tokens/s over all sequences and the HBM roofline fraction of the step."""
     import torch
@@ -455,7 +464,7 @@ def run_decode(shape, batch, ctx, steps, dev, world=1, rank=0, max_seq=None):
     from blackwell_b200.decode import DecodeEngine
 
     max_seq = max_seq or (ctx + 64)
-    eng = DecodeEngine(shape, batch, max_seq, dev, seed=3, world=world, rank=rank)
+    eng = DecodeEngine(shape, batch, max_seq, dev, seed=3, world=world, rank=rank, exchange=exchange)
     eng.fill_cache(ctx)
     gen = torch.Generator(device="cpu")
     gen.manual_seed(11)
@@ -497,6 +506,10 @@ def run_decode(shape, batch, ctx, steps, dev, world=1, rank=0, max_seq=None):
     from blackwell_b200 import kernels as k
 
     out["status"] = k.device_status()
+    if world > 1:
+        out["exchange"] = eng.exchange
+        if eng.peer is not None and eng.peer.status() != 0:
+            out["status"] = 3  # a peer all-reduce gave up waiting for another rank
     del eng, graph
     torch.cuda.empty_cache()
     return out
@@ -556,6 +569,8 @@ def main():
     ap.add_argument("--only", default=None, help="profiling aid: run one matrix of the set, NAME or NAME:ROWS")
     ap.add_argument("--attn-only", default=None, help="profiling aid: only the fp16-KV GQA decode attention kernel, "
                     "BATCH:CTX:NQH:NKV on a synthetic cache; prints its own JSON line")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1: how the K-split partial sums "
+                    "are summed across ranks (library NVLink peer-load all-reduce, or NCCL)")
     ap.add_argument("--tune", default=None, help="profiling aid: comma list of key=value for bw_set_tuning")
     args = ap.parse_args()
     global _ONLY
@@ -574,6 +589,12 @@ def main():
     if args.decode_only:
         import torch
 
+        if args.tune:
+            from blackwell_b200 import kernels as k
+
+            for kv in args.tune.split(","):
+                key, _, val = kv.partition("=")
+                k.set_tuning(int(key), int(val))
         model, b, c = args.decode_only.split(":")
         if world > 1:
             import torch.distributed as dist
@@ -582,7 +603,8 @@ def main():
             dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         torch.cuda.set_device(local_rank)
         shape = shapes.QWEN3_8B if model == "8b" else shapes.QWEN3_32B
-        out = run_decode(shape, int(b), int(c), args.steps, torch.device("cuda", local_rank), world, rank)
+        out = run_decode(shape, int(b), int(c), args.steps, torch.device("cuda", local_rank), world, rank,
+                         exchange=args.exchange)
         if rank == 0:
             print(json.dumps(out), flush=True)
         if world > 1:

@@ -14,6 +14,7 @@
 namespace bw {
 
 void set_attn_mma(int v);  // attention_decode.cu
+namespace peer { void set_two_step_min_kb(int kb); }  // peer_allreduce.cu
 
 namespace tc {  // tensor-core path, gemm_w4a8_tc.cu
 bool eligible(const GemvArgs& a, int M);
@@ -442,6 +443,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 7: tc::set_debug(value); return 0;
         case 8: g_pdl = value; return 0;
         case 9: set_attn_mma(value); return 0;
+        case 10: peer::set_two_step_min_kb(value); return 0;
         default: return cudaErrorInvalidValue;
     }
 }

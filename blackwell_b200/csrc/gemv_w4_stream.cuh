@@ -1,4 +1,4 @@
-// Streaming INT4 block-16 GEMV for small batch (M <= 8) on sm_100a.
+// Streaming INT4 block-16 GEMV for small batch (M <= 8 per launch) on sm_100a.
 //
 //   y[m][n] = sum_kb dot16(W[n,kb], x[m,kb]) * w_sc[n,kb] * x_sc[m,kb]
 //

@@ -30,11 +30,15 @@ ROPE_BASE = 1000000.0
 
 class DecodeEngine:
     def __init__(self, shape: ModelShape, batch: int, max_seq: int, device, seed: int = 0, world: int = 1,
-                 rank: int = 0, host_weights=None):
+                 rank: int = 0, host_weights=None, exchange: str = "nccl"):
         assert shape.head_dim == 128
         assert shape.n_q_heads % world == 0 and shape.n_kv_heads % world == 0, "heads must split evenly"
         self.s, self.M, self.max_seq, self.dev = shape, batch, max_seq, device
         self.world, self.rank = world, rank
+        # "nccl": torch.distributed all-reduce; "peer": the library's all-reduce over NVLink peer loads, the partial
+        # sums written by the GEMV straight into the exchanged buffer
+        assert exchange in ("nccl", "peer")
+        self.exchange = exchange if world > 1 else "nccl"
         self.nq = shape.n_q_heads // world
         self.nkv = shape.n_kv_heads // world
         H, I = shape.hidden, shape.inter
@@ -84,6 +88,13 @@ class DecodeEngine:
         self.tokens = torch.zeros((M,), dtype=torch.int32, device=dev)
         self.pos = torch.zeros((M,), dtype=torch.int32, device=dev)
         self.ctx_hint = max_seq
+        self.peer = None
+        if self.exchange == "peer":
+            from .peer import PeerComm
+
+            self.peer = PeerComm(world, rank, M * H, dev)
+            self.peer.connect_processes()
+            self.peer_slots = [self.peer.slot(0, M, H), self.peer.slot(1, M, H)]
         if world > 1:
             self.cand = torch.zeros((M, 2), dtype=f32, device=dev)
             self.cand_all = torch.zeros((world, M, 2), dtype=f32, device=dev)
@@ -110,10 +121,24 @@ class DecodeEngine:
     def set_tokens(self, ids):
         self.tokens.copy_(torch.as_tensor(ids, dtype=torch.int32))
 
-    def allreduce(self, t):
-        import torch.distributed as dist
+    def _partial_target(self):
+        """Where the K-split GEMV writes its partial sums: a local tensor (NCCL) or the next exchange slot."""
+        if self.peer is None:
+            return self.part
+        self._slot = self.peer.next_slot()
+        return self.peer_slots[self._slot]
 
-        dist.all_reduce(t)
+    def _exchange(self, part):
+        """Sums the partial results over the ranks; afterwards ``self.x`` holds the new hidden state on every rank.
+        A step makes an even number of exchanges (two per layer), so the slot order 0, 1, 0, 1 ... also holds across
+        replays of a captured step."""
+        if self.peer is None:
+            import torch.distributed as dist
+
+            dist.all_reduce(part)
+            self.x, self.part = self.part, self.x
+        else:
+            self.peer.allreduce(self._slot, self.x, self.M * self.s.hidden)
 
     def step(self):
         """Enqueues one decode step for the whole batch on the current stream."""
@@ -133,10 +158,10 @@ class DecodeEngine:
                                    self.nq * 128, H, M)
             else:
                 res = self.x if self.rank == 0 else None  # the residual enters the sum once
-                k.gemv_w4a8_decode(self.part, 0, res, self.attn, None, 0, None, 0.0, L["o"][0], L["o"][1],
+                part = self._partial_target()
+                k.gemv_w4a8_decode(part, 0, res, self.attn, None, 0, None, 0.0, L["o"][0], L["o"][1],
                                    self.nq * 128, H, M)
-                self.allreduce(self.part)
-                self.x, self.part = self.part, self.x
+                self._exchange(part)
             k.gemv_w4a8_decode(self.gu, 0, None, self.x, None, 0, L["rn_post"], eps, L["gu"][0], L["gu"][1], H,
                                2 * self.i_local, M)
             gate, up = self.gu, self.gu[:, self.i_local:]
@@ -145,10 +170,10 @@ class DecodeEngine:
                                    L["down"][1], self.i_local, H, M)
             else:
                 res = self.x if self.rank == 0 else None
-                k.gemv_w4a8_decode(self.part, 0, res, gate, up.data_ptr(), 2 * self.i_local, None, 0.0, L["down"][0],
+                part = self._partial_target()
+                k.gemv_w4a8_decode(part, 0, res, gate, up.data_ptr(), 2 * self.i_local, None, 0.0, L["down"][0],
                                    L["down"][1], self.i_local, H, M)
-                self.allreduce(self.part)
-                self.x, self.part = self.part, self.x
+                self._exchange(part)
         k.gemv_w4a8_decode(self.logits, 0, None, self.x, None, 0, self.rn_final, eps, self.lm[0], self.lm[1], H,
                            self.v_local, M)
         if self.world == 1:

@@ -67,19 +67,49 @@ def shard_gemv_set(mats, world: int, rank: int, head_dim: int = 128):
 
 
 class Collectives:
-    """The exchanges at the shard boundaries, on the current stream of ``device``."""
+    """The exchanges at the shard boundaries, on the current stream of ``device``.
 
-    def __init__(self, world: int, rank: int, device):
+    ``exchange="nccl"``: ``torch.distributed`` collectives.  ``exchange="peer"``: the K-split partial sums are written
+    by the GEMV into a peer-visible slot (``partial_buffer``) and summed by the library's NVLink all-reduce kernel;
+    consecutive K-split exchanges must alternate slots, which ``partial_buffer`` does in call order.
+    """
+
+    def __init__(self, world: int, rank: int, device, exchange: str = "nccl", slot_floats: int = 0):
         import torch.distributed as dist
 
+        assert exchange in ("nccl", "peer")
         self.world, self.rank, self.device = world, rank, device
         self.dist = dist
         self._gather_buf = {}
+        self.peer = None
+        self._k = {}          # shard name -> (slot, partial view, result tensor)
+        if exchange == "peer":
+            from .peer import PeerComm
+
+            self.peer = PeerComm(world, rank, slot_floats, device)
+            self.peer.connect_processes()
+
+    def partial_buffer(self, sh: Shard, M: int):
+        """The tensor a K-split GEMV of ``sh`` must write to, or None when any tensor will do (NCCL)."""
+        if self.peer is None or sh.kind != "k":
+            return None
+        import torch
+
+        if sh.name not in self._k:
+            slot = self.peer.next_slot()
+            self._k[sh.name] = (slot, self.peer.slot(slot, M, sh.N),
+                                torch.zeros((M, sh.N), dtype=torch.float32, device=self.device))
+        return self._k[sh.name][1]
 
     def finish(self, sh: Shard, y):
         """y: [M, n_local] fp32 (row kinds) or [M, N] partial sums (k kind).  Returns the tensor holding the
         complete result on every rank ([world, M, n_pad] for the gather)."""
         if sh.kind == "k":
+            if self.peer is not None:
+                slot, part, out = self._k[sh.name]
+                assert y.data_ptr() == part.data_ptr(), "the GEMV must write into partial_buffer()"
+                self.peer.allreduce(slot, out, out.numel())
+                return out
             self.dist.all_reduce(y)
             return y
         if sh.kind == "row_gather":

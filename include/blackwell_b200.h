@@ -45,23 +45,27 @@ int bw_gemv_int4_warp(float* y_out, const void* x_packed, const float* x_scale, 
 
 /* W4A8 GEMV: int8 activations (from bw_quantize_int8*), binary16 weight scales
  * (passed as uint16_t bit patterns).  Extension; arithmetic follows
- * src/kernels/gemv_int8.cu:937-965 with the int8 operand of :718-748. */
+ * src/kernels/gemv_int8.cu:937-965 with the int8 operand of :718-748.
+ * Any M >= 1.  Batch routing of all bw_gemv_w4a8* entry points: up to 7 sequences run in the streaming dp4a
+ * kernel; from 8 sequences on (K % 32 == 0, 16-byte aligned W and x) the tcgen05 kernel takes 64 sequences per
+ * launch; operands the tensor-core kernel cannot take fall back to dp4a passes of 8 (pre-quantized x only). */
 int bw_gemv_w4a8(float* y_out, const int8_t* x_q, const float* x_scale, const uint8_t* W_packed,
                  const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
 
 /* W4A8 GEMV with the activation quantizer fused into the prologue: x is
- * binary16 [M][K].  M <= 8, K % 32 == 0, 16-byte aligned pointers. */
+ * binary16 [M][K].  K % 32 == 0, 16-byte aligned pointers; any M >= 1 (see the routing note above; M > 8
+ * needs the tensor-core path's operand alignment, else cudaErrorInvalidValue). */
 int bw_gemv_w4a8_f16in(float* y_out, const uint16_t* x_f16, const uint8_t* W_packed, const uint16_t* W_scale_f16,
                        int K, int N, int M, void* stream);
 
 /* Same with f32 activations and an optional RMSNorm (norm_weight != NULL):
  * y = W . q8(rmsnorm(x) ) -- fuses fused_rmsnorm (kernels.h:117-133) +
- * quantize_int8 (kernels.h:526-531) + the GEMV.  M <= 8. */
+ * quantize_int8 (kernels.h:526-531) + the GEMV.  Same M rule as bw_gemv_w4a8_f16in. */
 int bw_gemv_w4a8_f32in(float* y_out, const float* x_f32, const float* norm_weight, float eps,
                        const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
 
 /* y = W . q8(silu(gate) * up): fuses apply_swiglu (kernels.h:155-160) +
- * quantize_int8 + the GEMV (the down projection).  M <= 8. */
+ * quantize_int8 + the GEMV (the down projection).  Same M rule as bw_gemv_w4a8_f16in. */
 int bw_gemv_w4a8_swiglu(float* y_out, const float* gate, const float* up, const uint8_t* W_packed,
                         const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
 
@@ -70,14 +74,15 @@ int bw_gemv_w4a8_swiglu(float* y_out, const float* gate, const float* up, const 
  * or SwiGLU + quantize (up != NULL, same stride as x) -- and an optional residual added to the result
  * (residual may alias y_out; both use y_stride, 0 = N).  It replaces, in one launch, the reference's
  * fused_rmsnorm / apply_swiglu + quantize + gemv + vector_add_fp32 sequences
- * (server/inference_server_int4_batched.cu:256-279).  M <= 8. */
+ * (server/inference_server_int4_batched.cu:256-279).  Same M rule as bw_gemv_w4a8_f16in. */
 int bw_gemv_w4a8_decode(float* y_out, long y_stride, const float* residual_or_null, const float* x_f32,
                         const float* up_or_null, long x_stride, const float* norm_weight_or_null, float eps,
                         const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
 
 /* Reference-format (W4A4, fp32 scales) GEMV with fused prologues: the int4
  * quantize rule of quantize_int4 (kernels.h:800-816) applied to x, to
- * rmsnorm(x) (norm_weight != NULL) or to silu(gate)*up (up != NULL).  M <= 8. */
+ * rmsnorm(x) (norm_weight != NULL) or to silu(gate)*up (up != NULL).  M <= 8 (fp32 scales stay on the dp4a
+ * kernel). */
 int bw_gemv_int4_fused(float* y_out, const float* x_f32, const float* up_or_null, const float* norm_weight_or_null,
                        float eps, const uint8_t* W_packed, const float* W_scale, int K, int N, int M, void* stream);
 
@@ -207,10 +212,33 @@ int bw_apply_repetition_penalty(float* logits, const int* recent, int num_recent
 /* Reads (and clears) the device status word: 0 = ok, 1 = a kernel gave up on a
  * bounded wait for a bulk copy.  Synchronises the device. */
 int bw_device_status(int* status_out);
+/* ---- Tensor-parallel exchange over peer memory (no counterpart in the reference, which is single-GPU) ----
+ * All-reduce of the K-split projections' partial sums across the GPUs of one box through NVLink peer loads.
+ * bw_peer_comm_create allocates this rank's region on the current device (two slots of slot_bytes; the GEMV writes
+ * its partial sums into bw_peer_comm_slot(comm, slot) directly).  Between processes the 64-byte handle from
+ * bw_peer_comm_handle is passed to every peer's bw_peer_comm_open; inside one process bw_peer_comm_attach links two
+ * communicators instead.  bw_peer_allreduce_f32 (n % 4 == 0, n * 4 <= slot_bytes, 16-byte aligned out/residual)
+ * enqueues one kernel: signal, bounded wait (~2 s, then status 3 from bw_peer_comm_status and no result), sum of
+ * every rank's slot in rank order (+ residual) into out.  Every rank must issue the same sequence of calls with
+ * alternating slot (0, 1, 0, ...); creation and teardown synchronise the device, the all-reduce itself allocates
+ * nothing and may be captured in a CUDA graph. */
+int bw_peer_comm_create(int world, int rank, size_t slot_bytes, void** comm_out);
+int bw_peer_comm_handle(void* comm, void* handle_out_64);
+int bw_peer_comm_open(void* comm, int peer_rank, const void* handle_64);
+int bw_peer_comm_attach(void* comm, int peer_rank, void* peer_comm_same_process);
+float* bw_peer_comm_slot(void* comm, int slot);
+int bw_peer_allreduce_f32(void* comm, int slot, float* out, const float* residual_or_null, size_t n, void* stream);
+int bw_peer_comm_status(void* comm, int* status_out);
+int bw_peer_comm_destroy(void* comm);
+
 /* Tuning knobs for experiments: key 0 = ring stages (0 = automatic),
  * key 1 = CTAs per SM cap (0 = automatic), key 2 = force the plain-load kernel,
  * key 3 = rows per thread group and tile cap, key 4 = threads per CTA target,
- * key 5 = smallest batch sent to the tensor-core kernel (0 = default 8), key 6 = its K-split (0 = automatic). */
+ * key 5 = smallest batch sent to the tensor-core kernel (0 = default 8), key 6 = its K-split (0 = automatic),
+ * key 7 = stage-skipping bit mask of the tensor-core kernel for timing ablations (results are wrong when non-zero;
+ * 0 = off), key 8 = programmatic dependent launch on (1, default) / off (0), key 9 = tensor-core attention kernel
+ * for the binary16 cache on (1, default) / off (0: scalar kernel, for comparison runs), key 10 = smallest vector in
+ * KiB that the peer all-reduce sums in two steps on four or more ranks (0 = default 256). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);

@@ -1,0 +1,83 @@
+"""Peer-memory all-reduce (csrc/peer_allreduce.cu) on two GPUs of one box, both driven from this process.
+
+Skipped on a single-GPU box.  The expected value is the fp32 sum in rank order, which the kernel must match bit for
+bit on both ranks (all ranks have to hold identical hidden states after the exchange).
+"""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _two_gpus():
+    return _gpus() >= 2
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_allreduce_ranks_bitwise(world):
+    """world 2: the one-step kernel; world 4: the 1.3 MB cases take the two-step (reduce, then store to all) kernel."""
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from blackwell_b200.peer import PeerComm
+
+    rows, cols = 64, 5120
+    comms = [PeerComm(world, r, rows * cols, torch.device("cuda", r)) for r in range(world)]
+    try:
+        for r in range(world):
+            for q in range(world):
+                if q != r:
+                    comms[r].attach(comms[q])
+        rng = np.random.default_rng(0xB200)
+        for it, (m, n) in enumerate([(1, 4096), (64, 5120), (8, 4096), (64, 5120), (3, 5120), (1, 4096)]):
+            slot = it & 1
+            parts = [rng.standard_normal((m, n)).astype(np.float32) for _ in range(world)]
+            resid = rng.standard_normal((m, n)).astype(np.float32) if it % 3 == 0 else None
+            outs = []
+            for r in range(world):
+                dev = torch.device("cuda", r)
+                with torch.cuda.device(dev):
+                    assert comms[r].next_slot() == slot
+                    comms[r].slot(slot, m, n).copy_(torch.from_numpy(parts[r]))
+                    outs.append(torch.empty((m, n), dtype=torch.float32, device=dev))
+            for r in range(world):   # both kernels are enqueued before either is waited for
+                dev = torch.device("cuda", r)
+                with torch.cuda.device(dev):
+                    res = None if resid is None else torch.from_numpy(resid).to(dev)
+                    comms[r].allreduce(slot, outs[r], m * n, residual=res)
+            for r in range(world):
+                torch.cuda.synchronize(r)
+            want = (resid if resid is not None else np.zeros((m, n), np.float32)).copy()
+            for r in range(world):
+                want = (want + parts[r]).astype(np.float32)
+            for r in range(world):
+                assert comms[r].status() == 0
+                got = outs[r].cpu().numpy()
+                assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (it, r)
+    finally:
+        for r in range(world):
+            torch.cuda.synchronize(r)
+        for c in comms:
+            c.close()
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs two GPUs")
+def test_peer_allreduce_rejects_bad_arguments():
+    from blackwell_b200.kernels import KernelError
+    from blackwell_b200.peer import PeerComm
+
+    c0 = PeerComm(2, 0, 4096, torch.device("cuda", 0))
+    try:
+        out = torch.empty(4096, dtype=torch.float32, device="cuda:0")
+        with pytest.raises(KernelError):      # the peer was never attached
+            c0.allreduce(0, out, 4096)
+        with pytest.raises(KernelError):      # larger than a slot
+            c0.allreduce(0, out, 8192)
+        with pytest.raises(KernelError):      # not a multiple of four floats
+            c0.allreduce(0, out, 4094)
+    finally:
+        c0.close()
