@@ -212,6 +212,29 @@ int bw_apply_repetition_penalty(float* logits, const int* recent, int num_recent
 /* Reads (and clears) the device status word: 0 = ok, 1 = a kernel gave up on a
  * bounded wait for a bulk copy.  Synchronises the device. */
 int bw_device_status(int* status_out);
+/* ---- Weight container of the INT4 servers ----
+ * <prefix>.int4_t = int32 header [K, N, 16, K/16, 1] + N*K/2 bytes of nibbles; <prefix>.scale_t = int32 header
+ * [0, 0, 0, K/16, N] + N*(K/16) float32; <name>.f32 = raw float32.  Writer in the reference:
+ * better-inference/gguf_convert.cpp:62-88; reader: upload_w4, server/inference_server_int4_batched.cu:32-45.
+ * Return 0 on success; -1 cannot open, -2 file shorter/longer than its header says, -3 inconsistent header,
+ * -4 bad argument, -5 write failed; the upload may also return a (positive) cudaError_t. */
+int bw_w4_file_write(const char* prefix, const uint8_t* packed, const float* scales, int K, int N);
+int bw_w4_file_dims(const char* prefix, int* K_out, int* N_out);
+int bw_w4_file_read(const char* prefix, uint8_t* packed_out, float* scales_out, int K, int N);
+/* One projection in device memory: the reference's DevW4 {K, N, d, sc} (server/inference_server_int4_batched.cu:31)
+ * plus the binary16 copy of the scales that the bw_gemv_w4a8* entry points take.  bw_w4_file_upload reads the two
+ * files, allocates with cudaMalloc and copies (a load-time call: it synchronises); bw_w4_free releases. */
+typedef struct bw_dev_w4 {
+    int K, N;
+    uint8_t* packed;      /* [N][K/2] */
+    float* scale_f32;     /* [N][K/16] or NULL */
+    uint16_t* scale_f16;  /* [N][K/16] binary16 bit patterns, or NULL */
+} bw_dev_w4;
+int bw_w4_file_upload(const char* prefix, int want_f32_scales, int want_f16_scales, bw_dev_w4* out);
+int bw_w4_free(bw_dev_w4* w);
+int bw_f32_file_write(const char* path, const float* data, size_t n);
+int bw_f32_file_read(const char* path, float* data_out, size_t n);
+
 /* ---- Tensor-parallel exchange over peer memory (no counterpart in the reference, which is single-GPU) ----
  * All-reduce of the K-split projections' partial sums across the GPUs of one box through NVLink peer loads.
  * bw_peer_comm_create allocates this rank's region on the current device (two slots of slot_bytes; the GEMV writes
