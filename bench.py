@@ -328,6 +328,13 @@ def run_ours(args, rank, world, local_rank):
             per = per_matrix_times(dev, M)
         except Exception as exc:
             per = [{"error": repr(exc)[:200]}]
+    # ---- configs[2]: the same five matrices at 2..64 sequences per call (graph replay of the set, 1 GPU)
+    sweep = []
+    if rank == 0 and world == 1 and not args.only and M == 1:
+        try:
+            sweep = batch_sweep(dev, state, mats)
+        except Exception as exc:
+            sweep = [{"error": repr(exc)[:200]}]
     if world > 1:
         barrier()
 
@@ -375,6 +382,7 @@ def run_ours(args, rank, world, local_rank):
                      "kernel": "gemv_w4_stream_kernel<1,half>", "nominal_frac": achieved / 8000.0},
         "cpu_baseline": cpu,
         "per_matrix": per,
+        "batch_sweep": sweep,
         "decode": decode,
     }
     print(json.dumps(line), flush=True)
@@ -453,6 +461,47 @@ def per_matrix_times(dev, M, reference_arm=False):
         out.append(rec)
         del Ws
         torch.cuda.empty_cache()
+    return out
+
+
+def batch_sweep(dev, state, mats):
+    """The five-matrix set at M = 2..64 sequences per call: one CUDA graph of the five launches per M, replayed;
+    bytes = the set's algorithmic bytes at that M.  M <= 7 runs the dp4a kernel, M >= 8 the tcgen05 kernel."""
+    import torch
+
+    from blackwell_b200 import kernels as k
+    from blackwell_b200 import synth
+
+    peak, _ = measured_peak()
+    out = []
+    for m in (2, 4, 8, 16, 32, 64):
+        xs = [synth.activations_f16_device(m, sh.k_local, 700 + i, device=dev) for i, (sh, *_r) in enumerate(state)]
+        ys = [torch.empty((m, sh.n_local), dtype=torch.float32, device=dev) for sh, *_r in state]
+
+        def step():
+            for (sh, W, sc, _x, _y), x, y in zip(state, xs, ys):
+                k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, m)
+
+        step()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 20
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / reps * 1e3
+        nbytes = set_bytes(mats, m)
+        out.append({"M": m, "us_per_step": round(us, 1), "gbs": round(nbytes / us / 1e3, 1),
+                    "roofline_frac": round(nbytes / us / 1e3 / peak, 3), "status": k.device_status()})
+        del g, xs, ys
     return out
 
 
