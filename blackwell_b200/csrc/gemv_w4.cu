@@ -261,6 +261,9 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
     p.smem = fixed + (size_t)S * stage;
     p.row_unit = 1;
     while ((p.row_unit * row_sc) % 16 != 0) p.row_unit *= 2;
+    // Every tile must start on a row whose scale bytes are 16-byte aligned in global memory (the bulk copy's rule):
+    // with one row per tile and a scale row of 8 mod 16 bytes, odd tiles would not.  Such shapes take the plain kernel.
+    if ((rg * p.G) % p.row_unit != 0) return p;
     p.n_rows = N - N % p.row_unit;
     p.ok = p.n_rows > 0;
     return p;

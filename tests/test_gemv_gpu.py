@@ -276,3 +276,20 @@ def test_linearity_and_determinism_at_full_size(k):
                                sc[rows].cpu().numpy().view(np.uint16))
     assert max_abs_rel(y1[:, rows].cpu().numpy(), ref) < 2e-5
     assert k.device_status() == 0
+
+
+def test_huge_k_scale_rows_not_16_byte_multiples(k):
+    """K so large that only one row fits a tile, with binary16 scale rows of 8196 bytes: tiles would start at rows whose
+    scales are not 16-byte aligned in global memory, which a bulk copy cannot fetch -- the planner must hand such a
+    shape to the plain-load kernel (it once planned one-row tiles for it)."""
+    import torch
+
+    M, K, N = 1, 65568, 12
+    W, sc16, _ = synth.int4_weights(N, K, 77)
+    x32 = synth.activations_f16(M, K, 78).astype(np.float32)
+    x8, x8s = oracle.quantize_int8(x32)
+    y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    k.gemv_w4a8(y, to_dev(x8), to_dev(x8s), to_dev(W), to_dev(sc16), K, N, M)
+    torch.cuda.synchronize()
+    assert max_abs_rel(y.cpu().numpy(), oracle.gemv_w4a8_f64(x8, x8s, W, sc16)) < 2e-5
+    assert k.device_status() == 0
