@@ -18,7 +18,8 @@ namespace tc {
 // Activation prep: quantizes every 16-element k-block of every sequence once (the same make_xblock code as the
 // streaming kernel's prologue: plain / RMSNorm / SwiGLU, int8 rule) and stores it in the layout the MMA's B
 // operand wants, chunk by chunk:
-//   chunk c: [block 0..15][row group 0..Mpad/8-1][8 rows][16 B]   then   [block 0..15][Mpad] float scales / 16
+//   chunk c: 8 block pairs, each [even block: Mpad rows x 16 B][Mpad rows of zeros][odd block]   then
+//            [block 0..15][Mpad] float scales / 16
 // Rows >= M and k-blocks >= K/16 are zero with scale 0.  Grid (ceil(nkb_pad / 256), Mpad), 256 threads.
 // ----------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) prep_x_kernel(unsigned char* xb, const GemvArgs a, int M, int Mpad,
@@ -54,8 +55,11 @@ __global__ void __launch_bounds__(256) prep_x_kernel(unsigned char* xb, const Ge
     if (m < M && kb < nkb) make_xblock(a, m, kb, rstd, e, o, s);
     const int c = kb / kBlocksPerChunk, b = kb % kBlocksPerChunk;
     unsigned char* chunk = xb + (size_t)c * xb_chunk_bytes(Mpad);
-    *reinterpret_cast<uint4*>(chunk + ((size_t)b * Mpad + m) * 16) = make_uint4(e[0], o[0], e[1], o[1]);
-    reinterpret_cast<float*>(chunk + (size_t)kBlocksPerChunk * Mpad * 16)[b * Mpad + m] = s;
+    // pair layout [even block][zeros][odd block], Mpad rows of 16 bytes each; the even block's thread writes the zeros
+    const size_t slot = (size_t)(b >> 1) * 3 + (size_t)(b & 1) * 2;
+    *reinterpret_cast<uint4*>(chunk + (slot * Mpad + m) * 16) = make_uint4(e[0], o[0], e[1], o[1]);
+    if ((b & 1) == 0) *reinterpret_cast<uint4*>(chunk + ((slot + 1) * Mpad + m) * 16) = make_uint4(0u, 0u, 0u, 0u);
+    reinterpret_cast<float*>(chunk + (size_t)b_chunk_bytes(Mpad))[b * Mpad + m] = s;
 }
 
 // ----------------------------------------------------------------------------------------------------------
@@ -68,7 +72,7 @@ __host__ __device__ constexpr int sub_chunks(int Mpad) { return Mpad > 0 ? 2 : 2
 __host__ __device__ constexpr int packed_slots(int Mpad) { return Mpad <= 16 ? 3 : 2; }
 // The activation ring runs deeper than the operand ring: its slots are refilled from L2 only after the MMAs that
 // read them retire, and with two slots that latency was the period of the whole pipeline.
-__host__ __device__ constexpr int b_slots(int Mpad) { return Mpad <= 32 ? 4 : 3; }
+__host__ __device__ constexpr int b_slots(int Mpad) { return Mpad <= 32 ? 4 : 2; }
 __host__ __device__ constexpr int s_slots(int Mpad) { return Mpad <= 32 ? 4 : 3; }
 __host__ __device__ constexpr int packed_slot_bytes(int Mpad) { return kRows * 128 * sub_chunks(Mpad); }
 
@@ -79,9 +83,8 @@ struct Smem {
     static constexpr int kLast = 520;
     static constexpr int kPacked = 1024;                                 // packed_slots x packed_slot_bytes
     __host__ __device__ static constexpr int a_off(int Mpad) { return kPacked + packed_slots(Mpad) * packed_slot_bytes(Mpad); }
-    __host__ __device__ static constexpr int zero_off(int Mpad) { return a_off(Mpad) + kSA * kAStageBytes; }  // after every A tile
-    __host__ __device__ static constexpr int b_off(int Mpad) { return zero_off(Mpad) + kZeroBytes; }
-    __host__ __device__ static constexpr int scales(int Mpad) { return b_off(Mpad) + b_slots(Mpad) * kBlocksPerChunk * Mpad * 16; }
+    __host__ __device__ static constexpr int b_off(int Mpad) { return a_off(Mpad) + kSA * kAStageBytes; }
+    __host__ __device__ static constexpr int scales(int Mpad) { return b_off(Mpad) + b_slots(Mpad) * b_chunk_bytes(Mpad); }
     __host__ __device__ static constexpr int scale_slot_bytes(int Mpad) { return kBlocksPerChunk * Mpad * 4; }  // x_sc / 16
     __host__ __device__ static constexpr int wscales(int Mpad) { return scales(Mpad) + s_slots(Mpad) * scale_slot_bytes(Mpad); }
     __host__ __device__ static constexpr int total(int Mpad) { return wscales(Mpad) + kSW * kWScaleBytes; }  // weight-scale ring
@@ -127,13 +130,14 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(smem + Smem::kTmemPtr);
     auto bar = [&](int i) { return smem_u32(&bars[i]); };
     auto wait = [&](int i, uint32_t parity) {
+        if (mbar_try_wait(bar(i), parity)) return true;   // the common case costs one probe
         if (*abort_flag) return false;
         if (!mbar_wait(bar(i), parity)) { *abort_flag = 1; return false; }
         return true;
     };
     const int s_off = Smem::scales(NMMA);
     const int s_slot = Smem::scale_slot_bytes(NMMA);
-    const int b_slot = kBlocksPerChunk * NMMA * 16;
+    const int b_slot = b_chunk_bytes(NMMA);
 
     if (t == 0) {
         for (int i = 0; i < 4; ++i) { mbar_init(bar(kFullP + i), 1); mbar_init(bar(kEmptyP + i), 4); }
@@ -145,12 +149,10 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
         *abort_flag = 0;
         mbar_fence_init();
     }
-    for (int i = t; i < kZeroBytes / 4; i += kThreads) reinterpret_cast<uint32_t*>(smem + Smem::zero_off(NMMA))[i] = 0u;
     if (warp == 0) {
         tmem_alloc(smem_u32(smem + Smem::kTmemPtr), 512);
         tmem_relinquish();
     }
-    fence_proxy_async();  // the zero region is read by the tensor core's shared-memory path
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -180,36 +182,26 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                     if (!wait(kEmptyS + ss, ((n / SS) & 1) ^ 1)) { ok = false; break; }
                     unsigned char* sslot = smem + s_off + ss * s_slot;
                     const unsigned char* xchunk = a.xb + (size_t)c * xb_chunk_bytes(NMMA);
-                    if (a.debug & 16) mbar_arrive(bar(kFullS + ss));
-                    else {
                     mbar_expect_tx(bar(kFullS + ss), s_slot);
                     bulk_g2s_plain(smem_u32(sslot), xchunk + b_slot, s_slot, bar(kFullS + ss));
-                    }
                     if (i % SUB == 0) {  // a new box: SUB chunks of packed nibbles at once
                         const int sp = np % SPS;
                         if (!wait(kEmptyP + sp, ((np / SPS) & 1) ^ 1)) { ok = false; break; }
-                        if (a.debug & 32) mbar_arrive(bar(kFullP + sp));
-                        else {
                         mbar_expect_tx(bar(kFullP + sp), PSLOT);
                         tma_load_2d(smem_u32(smem + Smem::kPacked + sp * PSLOT), &map_w, c * (kKc / 2) / a.map_elem,
                                     row0, bar(kFullP + sp));
-                        }
                         ++np;
                     }
                     if (!wait(kFreeB + sb, ((n / SB) & 1) ^ 1)) { ok = false; break; }
-                    if (a.debug & 16) mbar_arrive(bar(kFullB + sb));
-                    else {
                     mbar_expect_tx(bar(kFullB + sb), b_slot);
                     bulk_g2s_plain(smem_u32(smem + Smem::b_off(NMMA) + sb * b_slot), xchunk, b_slot, bar(kFullB + sb));
-                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = idesc_i8(NMMA);
-            const uint32_t zero_addr = smem_u32(smem + Smem::zero_off(NMMA));
+            const uint32_t idesc = idesc_i8(2 * NMMA);
             int gcount = 0, n = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
@@ -226,15 +218,14 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                         const int dg = gcount & 1;
                         if (!wait(kDEmpty + dg, ((gcount >> 1) & 1) ^ 1)) { ok = false; break; }
                         tc_fence_after();
-                        for (int bi = 0; bi < GB; ++bi) {
-                            if (a.debug & 4) break;
+                        // one MMA per pair of k-blocks: A's two K steps are the two blocks' tiles, B's the pair layout
+#pragma unroll
+                        for (int bi = 0; bi < GB; bi += 2) {
                             const int b = g * GB + bi;
                             const uint32_t a_addr = a_base + b * kABlockStride;
-                            // A: first K step = the block, second K step = the zero region
-                            const uint64_t da = smem_desc(a_addr, zero_addr - a_addr, 128);
-                            // B: first K step = the block; the second multiplies zeros, any valid rows will do
-                            const uint32_t b_addr = b_base + b * NMMA * 16;
-                            const uint64_t db = smem_desc(b_addr, b == kBlocksPerChunk - 1 ? 0 : NMMA * 16, 128);
+                            const uint64_t da = smem_desc(a_addr, kABlockStride, 128);
+                            const uint32_t b_addr = b_base + (b >> 1) * 3 * NMMA * 16;
+                            const uint64_t db = smem_desc(b_addr, NMMA * 16, 128);
                             tc_mma_i8(tmem + dg * 256 + bi * NMMA, da, db, idesc, 1u);
                         }
                         tc_commit(bar(kDFull + dg));
@@ -294,7 +285,6 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
             unsigned char* dst = smem + Smem::a_off(NMMA) + sa * kAStageBytes;
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
-                if (a.debug & 2) break;
                 const int gidx = it * 128 + ut;       // 16-byte chunk of the packed tile
                 const int row = gidx >> 3, cc = gidx & 7;
                 const uint4 w = *reinterpret_cast<const uint4*>(src + row * (128 * SUB) + cc * 16);
@@ -359,7 +349,6 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                         uint32_t v[PB][CW];
 #pragma unroll
                         for (int p = 0; p < PB; ++p) {
-                            if (a.debug & 8) break;
                             const uint32_t addr = lane_addr + dg * 256 + (bi + p) * NMMA;
                             if constexpr (CW == 8) {
                                 tmem_ld8(addr, v[p]);
@@ -389,7 +378,6 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                         }
 #pragma unroll
                         for (int p = 0; p < PB; ++p) {
-                            if (a.debug & 1) break;
                             const int b = g * GB + bi + p;              // k-block within the chunk
                             const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&wcur[b >> 1]));
                             const float w = (b & 1) ? wf.y : wf.x;
@@ -506,9 +494,8 @@ static cudaError_t tc_scratch(size_t bytes, unsigned char** out) {
 }
 
 static int g_tc_ksplit_override = 0;
-static int g_tc_debug = 0;
 void set_ksplit_override(int v) { g_tc_ksplit_override = v; }
-void set_debug(int v) { g_tc_debug = v; }
+void set_debug(int) {}  // the stage-skipping switches of the timing ablations are no longer compiled in
 
 int read_clear_status() {
     int v = 0;
@@ -587,7 +574,7 @@ cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st) {
     t.nkb = a.K / 16;
     t.partial = reinterpret_cast<float*>(scratch + part_off);
     t.tickets = reinterpret_cast<unsigned int*>(scratch);
-    t.N = a.N; t.M = M; t.Mpad = Mpad; t.nchunks = nchunks; t.ksplit = ksplit; t.map_elem = 4; t.debug = g_tc_debug;
+    t.N = a.N; t.M = M; t.Mpad = Mpad; t.nchunks = nchunks; t.ksplit = ksplit; t.map_elem = 4;
     const int grid = tiles * ksplit < sms ? tiles * ksplit : sms;  // persistent: one CTA per SM at most
     if (Mpad == 16) return launch_n<16>(map_w, t, grid, st);
     if (Mpad == 32) return launch_n<32>(map_w, t, grid, st);

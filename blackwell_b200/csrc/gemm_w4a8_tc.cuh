@@ -40,7 +40,6 @@ constexpr int kABlockStride = 2048 + 16;  // bytes between the int8 tiles of con
 constexpr int kPackedBytes = kRows * (kKc / 2);                  // 16384
 constexpr int kWScaleBytes = kRows * kBlocksPerChunk * 2;        // 4096
 constexpr int kAStageBytes = kBlocksPerChunk * kABlockStride;    // 33024
-constexpr int kZeroBytes = 2048;
 constexpr int kThreads = 512;
 
 struct TcArgs {
@@ -55,12 +54,16 @@ struct TcArgs {
     int N, M, Mpad;           // Mpad = MMA N in {16, 32, 64}
     int nchunks;              // ceil(K / 256)
     int ksplit;               // CTAs sharing one row tile
-    int debug;                // timing experiments (bit 1: no scaling, 2: no unpack, 4: no MMA, 8: no TMEM loads)
     int map_elem;             // bytes per element of the weight tensor map (its x coordinate is in elements)
 };
 
-// bytes of one activation chunk in global memory: 16 blocks x Mpad rows x 16 B, then 16 x Mpad block scales
-__host__ __device__ inline size_t xb_chunk_bytes(int Mpad) { return (size_t)kBlocksPerChunk * Mpad * 16 + (size_t)kBlocksPerChunk * Mpad * 4; }
+// B operand of one chunk: 8 block pairs, each [block 2p: Mpad rows x 16 B][Mpad rows of zeros][block 2p + 1].
+// One MMA (K = 32) takes a pair: its first K step reads rows [0, 2 Mpad) from the start of the pair (block 2p, then
+// the zeros), its second K step the same number of rows starting at the zeros (zeros, then block 2p + 1), so the
+// accumulator columns [0, Mpad) hold the dots of block 2p and [Mpad, 2 Mpad) those of block 2p + 1.
+__host__ __device__ constexpr int b_chunk_bytes(int Mpad) { return (kBlocksPerChunk / 2) * 3 * Mpad * 16; }
+// bytes of one activation chunk in global memory: the B operand, then 16 x Mpad block scales
+__host__ __device__ inline size_t xb_chunk_bytes(int Mpad) { return (size_t)b_chunk_bytes(Mpad) + (size_t)kBlocksPerChunk * Mpad * 4; }
 
 // ------------------------------------------------------------------ tcgen05 wrappers
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {

@@ -258,10 +258,9 @@ int bw_peer_comm_destroy(void* comm);
  * key 1 = CTAs per SM cap (0 = automatic), key 2 = force the plain-load kernel,
  * key 3 = rows per thread group and tile cap, key 4 = threads per CTA target,
  * key 5 = smallest batch sent to the tensor-core kernel (0 = default 8), key 6 = its K-split (0 = automatic),
- * key 7 = stage-skipping bit mask of the tensor-core kernel for timing ablations (results are wrong when non-zero;
- * 0 = off), key 8 = programmatic dependent launch on (1, default) / off (0), key 9 = tensor-core attention kernel
+ * key 7 = unused (accepted, no effect), key 8 = programmatic dependent launch on (1, default) / off (0), key 9 = tensor-core attention kernel
  * for the binary16 cache on (1, default) / off (0: scalar kernel, for comparison runs), key 10 = smallest vector in
- * KiB that the peer all-reduce sums in two steps on four or more ranks (0 = default 256). */
+ * KiB that the peer all-reduce sums in two steps on four or more ranks (0 = default 4096). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);

@@ -25,6 +25,9 @@ def test_peer_allreduce_ranks_bitwise(world):
         pytest.skip(f"needs {world} GPUs")
     from blackwell_b200.peer import PeerComm
 
+    from blackwell_b200 import kernels as k
+
+    k.set_tuning(10, 256)   # vectors of 256 KiB and more take the two-step kernel on 4+ ranks (default: 4 MiB)
     rows, cols = 64, 5120
     comms = [PeerComm(world, r, rows * cols, torch.device("cuda", r)) for r in range(world)]
     try:
@@ -59,6 +62,7 @@ def test_peer_allreduce_ranks_bitwise(world):
                 got = outs[r].cpu().numpy()
                 assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (it, r)
     finally:
+        k.set_tuning(10, 0)
         for r in range(world):
             torch.cuda.synchronize(r)
         for c in comms:
