@@ -283,17 +283,29 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
             if (!wait(kFreeAB + sa, ((n / kSA) & 1) ^ 1)) { ok = false; break; }
             const unsigned char* src = smem + Smem::kPacked + sp * PSLOT + sub * 128;
             unsigned char* dst = smem + Smem::a_off(NMMA) + sa * kAStageBytes;
+            // All eight loads are issued before the first store: source and destination are both shared memory, so the
+            // compiler would otherwise keep every load behind the previous iteration's stores and the loop would run
+            // at one shared-memory round trip per iteration.
+            // A quarter warp (one shared-memory phase of a 16-byte access) takes eight rows on a diagonal of 16-byte
+            // columns: its reads fall in eight different bank groups (the column) and so do its writes (the row within
+            // its group of eight).  With rows-then-columns order the stores hit every bank group four times.
+            const int j = ut & 7, dg8 = (ut >> 3) & 7, rhi = ut >> 6;
+            const int cc = (j + dg8) & 7;
+            uint4 wv[8];
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
-                const int gidx = it * 128 + ut;       // 16-byte chunk of the packed tile
-                const int row = gidx >> 3, cc = gidx & 7;
-                const uint4 w = *reinterpret_cast<const uint4*>(src + row * (128 * SUB) + cc * 16);
+                const int row = (rhi + 2 * it) * 8 + j;
+                wv[it] = *reinterpret_cast<const uint4*>(src + row * (128 * SUB) + cc * 16);
+            }
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const uint4 w = wv[it];
                 uint4 o0, o1;
                 nibbles_to_s8x16(w.x, o0.x, o0.y);
                 nibbles_to_s8x16(w.y, o0.z, o0.w);
                 nibbles_to_s8x16(w.z, o1.x, o1.y);
                 nibbles_to_s8x16(w.w, o1.z, o1.w);
-                unsigned char* d0 = dst + (2 * cc) * kABlockStride + (row >> 3) * 128 + (row & 7) * 16;
+                unsigned char* d0 = dst + (2 * cc) * kABlockStride + (rhi + 2 * it) * 128 + j * 16;
                 *reinterpret_cast<uint4*>(d0) = o0;
                 *reinterpret_cast<uint4*>(d0 + kABlockStride) = o1;
             }
