@@ -132,3 +132,52 @@ def write_synthetic_tree(root: str, shape: ModelShape, seed: int = 0, vocab: int
         total += packed.nbytes + 4 * sc16.size + 40
     write_f32(os.path.join(root, "final_norm.f32"), synth.norm_weight(shape.hidden, seed + 90003))
     return total + qk.nbytes + 4 * shape.hidden
+
+
+def _byte_encoder_codepoints():
+    """The byte -> unicode codepoint table of byte-level BPE (printable bytes map to themselves, the rest to 256+)."""
+    keep = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+    cps, extra = [0] * 256, 0
+    for b in range(256):
+        if b in keep:
+            cps[b] = b
+        else:
+            cps[b] = 256 + extra
+            extra += 1
+    return cps
+
+
+def write_synthetic_tokenizer(path: str, vocab: int):
+    """A minimal ``tokenizer_data.bin`` in the layout ``BpeTokenizer::load`` reads (include/blackwell/bpe_tokenizer.h:
+    168-296): header (vocab, merges, added), 256 byte-encoder codepoints, vocab entries (id u32, length u16, UTF-8),
+    no added tokens, no merges.  Ids 0..255 are the single bytes; every other id decodes to the text ``<id>``, so
+    that generated text shows the generated ids."""
+    import struct
+
+    cps = _byte_encoder_codepoints()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<3I", vocab, 0, 0))
+        f.write(struct.pack("<256I", *cps))
+        for i in range(vocab):
+            s = chr(cps[i]).encode("utf-8") if i < 256 else b"<%d>" % i
+            f.write(struct.pack("<IH", i, len(s)))
+            f.write(s)
+
+
+def write_linked_tree(root: str, shape: ModelShape, seed: int = 0):
+    """A full-size tree at the disk cost of one layer: layer 0 and the embedding are written, every other layer and
+    ``lm_head`` are hard links to them (synthetic weights carry no meaning, the loaders only need the files)."""
+    one = ModelShape(shape.name, 1, shape.hidden, shape.inter, shape.n_q_heads, shape.n_kv_heads, shape.head_dim,
+                     shape.vocab, shape.eps)
+    write_synthetic_tree(root, one, seed)
+    for l in range(1, shape.layers):
+        for name in PROJECTIONS:
+            for ext in (".int4_t", ".scale_t"):
+                os.link(os.path.join(root, f"0_{name}{ext}"), os.path.join(root, f"{l}_{name}{ext}"))
+        for name in ("input_layernorm", "post_attention_layernorm"):
+            os.link(os.path.join(root, f"0_{name}.f32"), os.path.join(root, f"{l}_{name}.f32"))
+    qk = read_f32(os.path.join(root, "qk_norms.f32"), 2 * shape.head_dim)
+    write_f32(os.path.join(root, "qk_norms.f32"), np.tile(qk, shape.layers))
+    for ext in (".int4_t", ".scale_t"):
+        os.remove(os.path.join(root, "lm_head" + ext))
+        os.link(os.path.join(root, "embed_tokens" + ext), os.path.join(root, "lm_head" + ext))
