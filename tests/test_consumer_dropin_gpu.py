@@ -58,3 +58,50 @@ def test_reference_text_generator_runs_on_both_libraries(cuda, tmp_path):
     assert prefix >= 4, (ours[0], ref[0])
     for lines in (ours, ref):                            # same prompt, same continuation within a run
         assert all(l.split("] ", 1)[1] == lines[0].split("] ", 1)[1] for l in lines)
+
+
+SRV_OURS = os.path.join(REFDIR, "inference_server_int4_batched_ours")
+SRV_REF = os.path.join(REFDIR, "inference_server_int4_batched_ref")
+
+
+def _ask_daemon(exe, cwd, request):
+    """Starts the reference's stdin/stdout JSON daemon, sends one request line, reads one response line and stops the
+    process (it has no shutdown command and spins on end-of-file, so it is never left to read a closed pipe)."""
+    import json
+
+    p = subprocess.Popen([exe], cwd=cwd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    try:
+        p.stdin.write(request + "\n")
+        p.stdin.flush()
+        line = p.stdout.readline()
+    finally:
+        p.kill()
+        p.wait(timeout=60)
+    assert line.strip(), p.stderr.read()[-1500:]
+    return json.loads(line)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.skipif(not (os.path.exists(SRV_OURS) and os.path.exists(SRV_REF)), reason="oracle/_ref daemons not built")
+def test_reference_json_daemon_runs_on_both_libraries(cuda, tmp_path):
+    """server/inference_server_int4_batched.cu, unmodified: one request over its JSON-lines protocol
+    (:340-384), two prompts, greedy."""
+    from blackwell_b200 import weight_files as wf
+    from blackwell_b200.shapes import ModelShape
+
+    shape = ModelShape("consumer-8b", layers=36, hidden=4096, inter=12288, n_q_heads=32, n_kv_heads=8, head_dim=128,
+                       vocab=151936)
+    wf.write_linked_tree(str(tmp_path / "weights_int4_qwen3_8b"), shape, seed=123)
+    wf.write_synthetic_tokenizer(str(tmp_path / "tokenizer_data.bin"), shape.vocab)
+    req = '{"prompts": ["The capital of France is", "Two plus two is"], "max_tokens": 8, "temperature": 0.0}'
+    ours = _ask_daemon(SRV_OURS, str(tmp_path), req)
+    ref = _ask_daemon(SRV_REF, str(tmp_path), req)
+    assert len(ours["tokens"]) == 2 and len(ref["tokens"]) == 2 and len(ours["text"]) == 2
+    for a in ours["tokens"]:
+        assert len(a) == 8 and all(0 <= t < shape.vocab for t in a)
+    # With this library the daemon starts the first prompt exactly like the text generator above does with either
+    # library (ids 47388, 48015, 118878 for this seed).  The reference's own kernels do not reproduce that in the daemon
+    # (its attention runs with a 4096-position cache here, 512 in the generator): reported, not asserted.
+    assert ours["tokens"][0][:3] == [47388, 48015, 118878], ours["tokens"][0]
+    print("daemon, this library:", ours["tokens"])
+    print("daemon, reference kernels:", ref["tokens"])
