@@ -630,6 +630,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        # torchrun exports OMP_NUM_THREADS=1 to every rank; the reference arm is one process that should use every host
+        # core (the variable is read when the oracle's OpenMP runtime starts, which has not happened yet)
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
         run_reference(args, rank)
         return
     if args.attn_only:
