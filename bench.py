@@ -287,13 +287,26 @@ def run_ours(args, rank, world, local_rank):
     h2d = sum(h.numel() * 2 for h in host_x)
     d2h = sum(h.numel() * 4 for h in host_y)
 
+    # The caller's pipeline: inputs go up first, the largest matrix (the LM head) runs first and every result travels
+    # back on a second stream while the next matrices compute, so only the last, small result's copy is exposed.
+    copy_stream = torch.cuda.Stream(device=dev)
+    e2e_order = sorted(range(len(state)), key=lambda i: -state[i][0].n_local * state[i][0].k_local)
+
     def e2e_enqueue():
-        for hx, hy, (sh, W, sc, x, y) in zip(host_x, host_y, state):
-            x.copy_(hx, non_blocking=True)
+        main = torch.cuda.current_stream()
+        for i in e2e_order:
+            state[i][3].copy_(host_x[i], non_blocking=True)
+        for i in e2e_order:
+            sh, W, sc, x, y = state[i]
             k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
             if coll is not None and sh.kind == "k":
                 y = coll.finish(sh, y)
-            hy.copy_(y, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(main)
+            copy_stream.wait_event(done)
+            with torch.cuda.stream(copy_stream):
+                host_y[i].copy_(y, non_blocking=True)
+        main.wait_stream(copy_stream)
 
     if use_graph:
         e2e_graph = torch.cuda.CUDAGraph()
