@@ -55,6 +55,60 @@ struct AttnArgs {
 // Partial record of one (sequence, head, split): 128 un-normalised outputs, then max and sum.
 constexpr int kPartStride = kHd + 2;
 
+// With arrival counters the CTA that finishes a (sequence, kv head) last merges all its splits itself; no second
+// launch.  One warp per head: lanes first run over the splits (maxima, weights, sum), then over the 128 outputs,
+// four each, with the split weights broadcast by shuffle; every record load is independent.  Called by all
+// threads of the CTA after its own partial records are written.
+template <int GQ>
+__device__ __forceinline__ void last_arriver_merge(const AttnArgs& a, int m, int kvh, int h0, int* s_last) {
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    __threadfence();
+    __syncthreads();
+    if (t == 0) *s_last = (atomicAdd(&a.tickets[m * a.nkv + kvh], 1u) == (unsigned)a.nsplit - 1) ? 1 : 0;
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    for (int h = warp; h < GQ; h += kAttnWarps) {
+        const size_t head = (size_t)m * a.nqh + h0 + h;
+        const float* base = a.part + head * a.nsplit * kPartStride;
+        float mloc = -FLT_MAX;
+        for (int s = lane; s < a.nsplit; s += 32)
+            if (__ldcg(base + (size_t)s * kPartStride + kHd + 1) > 0.f)
+                mloc = fmaxf(mloc, __ldcg(base + (size_t)s * kPartStride + kHd));
+        const float mall = warp_max(mloc);
+        float lsum = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < a.nsplit; s0 += 32) {
+            const int s = s0 + lane;
+            float c = 0.f;
+            if (s < a.nsplit) {
+                const float ls = __ldcg(base + (size_t)s * kPartStride + kHd + 1);
+                if (ls > 0.f) {
+                    c = __expf(__ldcg(base + (size_t)s * kPartStride + kHd) - mall);
+                    lsum = fmaf(ls, c, lsum);
+                }
+            }
+            const int cnt = min(32, a.nsplit - s0);
+#pragma unroll 4
+            for (int j = 0; j < cnt; ++j) {
+                const float cj = __shfl_sync(0xffffffffu, c, j);
+                if (cj != 0.f) {
+                    const float* rec = base + (size_t)(s0 + j) * kPartStride + 4 * lane;
+                    const float2 r0 = __ldcg(reinterpret_cast<const float2*>(rec));
+                    const float2 r1 = __ldcg(reinterpret_cast<const float2*>(rec + 2));
+                    acc.x = fmaf(cj, r0.x, acc.x); acc.y = fmaf(cj, r0.y, acc.y);
+                    acc.z = fmaf(cj, r1.x, acc.z); acc.w = fmaf(cj, r1.y, acc.w);
+                }
+            }
+        }
+        lsum = warp_sum(lsum);
+        const float inv = 1.0f / (lsum + 1e-9f);
+        *reinterpret_cast<float4*>(a.out + head * kHd + 4 * lane) =
+            make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    }
+    if (t == 0) a.tickets[m * a.nkv + kvh] = 0;
+}
+
 template <typename KVT, int GQ>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_split_kernel(const AttnArgs a) {
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
@@ -64,7 +118,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_split_kernel(cons
     const int seq_pos = a.d_seq_pos ? a.d_seq_pos[a.per_seq ? m : 0] : a.seq_pos;
     const int npos = min(seq_pos + 1, a.max_seq);
     const int p0 = split * a.split_len;
-    const int p1 = min(npos, p0 + a.split_len);
+    // The last split runs to the sequence's own end: the split length is sized from a hint of the context, and a
+    // sequence that has grown past the hint must still see all its positions.
+    const int p1 = split == a.nsplit - 1 ? npos : min(npos, p0 + a.split_len);
 
     const KVT* Kb = static_cast<const KVT*>(a.K) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
                     (size_t)kvh * a.max_seq * kHd;
@@ -166,58 +222,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_split_kernel(cons
     };
     merge_warps_and_emit(a.nsplit == 1);
 
-    // With arrival counters the CTA that finishes a (sequence, kv head) last merges all its splits itself, each
-    // warp folding a quarter of the records into a fresh online-softmax state; no second launch.
-    if (a.nsplit > 1 && a.tickets) {
-        __threadfence();
-        __syncthreads();
-        if (t == 0) s_last = (atomicAdd(&a.tickets[m * a.nkv + kvh], 1u) == (unsigned)a.nsplit - 1) ? 1 : 0;
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-            // One warp per head: lanes first run over the splits (maxima, weights, sum), then over the 128
-            // outputs, four each, with the split weights broadcast by shuffle; every record load is independent.
-            for (int h = warp; h < GQ; h += kAttnWarps) {
-                const size_t head = (size_t)m * a.nqh + h0 + h;
-                const float* base = a.part + head * a.nsplit * kPartStride;
-                float mloc = -FLT_MAX;
-                for (int s = lane; s < a.nsplit; s += 32)
-                    if (__ldcg(base + (size_t)s * kPartStride + kHd + 1) > 0.f)
-                        mloc = fmaxf(mloc, __ldcg(base + (size_t)s * kPartStride + kHd));
-                const float mall = warp_max(mloc);
-                float lsum = 0.f;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int s0 = 0; s0 < a.nsplit; s0 += 32) {
-                    const int s = s0 + lane;
-                    float c = 0.f;
-                    if (s < a.nsplit) {
-                        const float ls = __ldcg(base + (size_t)s * kPartStride + kHd + 1);
-                        if (ls > 0.f) {
-                            c = __expf(__ldcg(base + (size_t)s * kPartStride + kHd) - mall);
-                            lsum = fmaf(ls, c, lsum);
-                        }
-                    }
-                    const int cnt = min(32, a.nsplit - s0);
-#pragma unroll 4
-                    for (int j = 0; j < cnt; ++j) {
-                        const float cj = __shfl_sync(0xffffffffu, c, j);
-                        if (cj != 0.f) {
-                            const float* rec = base + (size_t)(s0 + j) * kPartStride + 4 * lane;
-                            const float2 r0 = __ldcg(reinterpret_cast<const float2*>(rec));
-                            const float2 r1 = __ldcg(reinterpret_cast<const float2*>(rec + 2));
-                            acc.x = fmaf(cj, r0.x, acc.x); acc.y = fmaf(cj, r0.y, acc.y);
-                            acc.z = fmaf(cj, r1.x, acc.z); acc.w = fmaf(cj, r1.y, acc.w);
-                        }
-                    }
-                }
-                lsum = warp_sum(lsum);
-                const float inv = 1.0f / (lsum + 1e-9f);
-                *reinterpret_cast<float4*>(a.out + head * kHd + 4 * lane) =
-                    make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-            }
-            if (t == 0) a.tickets[m * a.nkv + kvh] = 0;
-        }
-    }
+    if (a.nsplit > 1 && a.tickets) last_arriver_merge<GQ>(a, m, kvh, h0, &s_last);
 }
 
 // Tensor-core variant for the binary16 cache (see attention_mma.cuh): same grid, same splits, same partial records
@@ -231,7 +236,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const 
     const int seq_pos = a.d_seq_pos ? a.d_seq_pos[a.per_seq ? m : 0] : a.seq_pos;
     const int npos = min(seq_pos + 1, a.max_seq);
     const int p0 = split * a.split_len;
-    const int p1 = min(npos, p0 + a.split_len);
+    // The last split runs to the sequence's own end: the split length is sized from a hint of the context, and a
+    // sequence that has grown past the hint must still see all its positions.
+    const int p1 = split == a.nsplit - 1 ? npos : min(npos, p0 + a.split_len);
     const __half* Kb = static_cast<const __half*>(a.K) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
                        (size_t)kvh * a.max_seq * kHd;
     const __half* Vb = static_cast<const __half*>(a.V) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
@@ -281,54 +288,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const 
             if (d == 0) { rec[kHd] = mm; rec[kHd + 1] = ls; }
         }
     }
-    if (a.nsplit > 1 && a.tickets) {
-        __threadfence();
-        __syncthreads();
-        if (t == 0) s_last = (atomicAdd(&a.tickets[m * a.nkv + kvh], 1u) == (unsigned)a.nsplit - 1) ? 1 : 0;
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-            for (int h = warp; h < GQ; h += kAttnWarps) {
-                const size_t head = (size_t)m * a.nqh + h0 + h;
-                const float* base = a.part + head * a.nsplit * kPartStride;
-                float mloc = -FLT_MAX;
-                for (int s = lane; s < a.nsplit; s += 32)
-                    if (__ldcg(base + (size_t)s * kPartStride + kHd + 1) > 0.f)
-                        mloc = fmaxf(mloc, __ldcg(base + (size_t)s * kPartStride + kHd));
-                const float mall = warp_max(mloc);
-                float lsum = 0.f;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int s0 = 0; s0 < a.nsplit; s0 += 32) {
-                    const int s = s0 + lane;
-                    float c = 0.f;
-                    if (s < a.nsplit) {
-                        const float ls = __ldcg(base + (size_t)s * kPartStride + kHd + 1);
-                        if (ls > 0.f) {
-                            c = __expf(__ldcg(base + (size_t)s * kPartStride + kHd) - mall);
-                            lsum = fmaf(ls, c, lsum);
-                        }
-                    }
-                    const int cnt = min(32, a.nsplit - s0);
-#pragma unroll 4
-                    for (int j = 0; j < cnt; ++j) {
-                        const float cj = __shfl_sync(0xffffffffu, c, j);
-                        if (cj != 0.f) {
-                            const float* rec = base + (size_t)(s0 + j) * kPartStride + 4 * lane;
-                            const float2 r0 = __ldcg(reinterpret_cast<const float2*>(rec));
-                            const float2 r1 = __ldcg(reinterpret_cast<const float2*>(rec + 2));
-                            acc.x = fmaf(cj, r0.x, acc.x); acc.y = fmaf(cj, r0.y, acc.y);
-                            acc.z = fmaf(cj, r1.x, acc.z); acc.w = fmaf(cj, r1.y, acc.w);
-                        }
-                    }
-                }
-                lsum = warp_sum(lsum);
-                const float inv = 1.0f / (lsum + 1e-9f);
-                *reinterpret_cast<float4*>(a.out + head * kHd + 4 * lane) =
-                    make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-            }
-            if (t == 0) a.tickets[m * a.nkv + kvh] = 0;
-        }
-    }
+    if (a.nsplit > 1 && a.tickets) last_arriver_merge<GQ>(a, m, kvh, h0, &s_last);
 }
 
 // Merges the per-split partial records of one (sequence, head).
@@ -359,6 +319,7 @@ __global__ void __launch_bounds__(256) update_kv_kernel_b200(KVT* kc, KVT* vc, c
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= nh * hd) return;
     const int pos = d_pos ? *d_pos : pos_value;
+    if ((unsigned)pos >= (unsigned)max_seq) return;  // a position outside the cache is never written
     const int h = idx / hd, d = idx - h * hd;
     const size_t off = (size_t)h * max_seq * hd + (size_t)pos * hd + d;
     kc[off] = (KVT)k_new[idx];
@@ -366,33 +327,13 @@ __global__ void __launch_bounds__(256) update_kv_kernel_b200(KVT* kc, KVT* vc, c
 }
 
 // ------------------------------------------------------------------ host side
-struct Scratch {
-    float* ptr = nullptr;
-    size_t bytes = 0;
-};
-static Scratch g_scratch[kMaxDevices];
 static int g_attn_mma = 1;  // 0: keep the scalar kernel for the binary16 cache too (comparison runs)
 void set_attn_mma(int v) { g_attn_mma = v; }
-static std::mutex g_scratch_mu;
-
-// Grow-only per-device scratch for the split partials.  Growing frees and
-// reallocates (synchronising); it happens on the first call and when a larger
-// problem arrives, never in steady state.
-static cudaError_t attn_scratch(size_t bytes, float** out) {
-    std::lock_guard<std::mutex> lk(g_scratch_mu);
-    Scratch& s = g_scratch[current_device()];
-    if (s.bytes < bytes) {
-        if (s.ptr) cudaFree(s.ptr);
-        s.ptr = nullptr; s.bytes = 0;
-        size_t want = bytes < (size_t)(4 << 20) ? (size_t)(4 << 20) : bytes;
-        cudaError_t e = cudaMalloc(&s.ptr, want);
-        if (e != cudaSuccess) return e;
-        e = cudaMemset(s.ptr, 0, want);  // the arrival counters at the front must start at zero
-        if (e != cudaSuccess) return e;
-        s.bytes = want;
-    }
-    *out = s.ptr;
-    return cudaSuccess;
+// Per-device scratch for the split partials and arrival counters.
+static GrowScratch g_attn_scratch;
+cudaError_t attn_reserve_scratch(size_t bytes) {
+    unsigned char* p = nullptr;
+    return bytes ? g_attn_scratch.get(bytes, (size_t)4 << 20, nullptr, &p) : cudaSuccess;
 }
 
 // Number of context splits: the grid is (sequence, kv head) pairs x splits, `slots` CTAs are resident at a time, and a
@@ -417,6 +358,13 @@ static int choose_splits(int pairs, int ctx, int slots) {
     return best;
 }
 
+// Upper bound of the scratch a call with up to M sequences and a context hint up to ctx can need.
+size_t attn_scratch_bytes(int M, int nqh, int nkv, int ctx) {
+    if (M < 1 || nqh < 1 || nkv < 1 || ctx < 1) return 0;
+    const size_t tick_bytes = (((size_t)M * nkv * sizeof(unsigned int)) + 255) & ~(size_t)255;
+    return tick_bytes + (size_t)M * nqh * 64 * kPartStride * sizeof(float);  // at most 64 splits
+}
+
 template <typename KVT>
 static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     if (!a.out || !a.Q || !a.K || !a.V || a.nqh < 1 || a.nkv < 1 || a.nqh % a.nkv != 0 || a.M < 1 || a.max_seq < 1)
@@ -437,11 +385,12 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     if (nsplit > 1) {
         // scratch = [arrival counters, one per (sequence, kv head)] [partial records]
         const size_t tick_bytes = (((size_t)a.M * a.nkv * sizeof(unsigned int)) + 255) & ~(size_t)255;
-        float* base = nullptr;
-        cudaError_t e = attn_scratch(tick_bytes + (size_t)a.M * a.nqh * nsplit * kPartStride * sizeof(float), &base);
+        unsigned char* base = nullptr;
+        cudaError_t e = g_attn_scratch.get(tick_bytes + (size_t)a.M * a.nqh * nsplit * kPartStride * sizeof(float),
+                                           (size_t)4 << 20, st, &base);
         if (e != cudaSuccess) return e;
         a.tickets = reinterpret_cast<unsigned int*>(base);
-        a.part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(base) + tick_bytes);
+        a.part = reinterpret_cast<float*>(base + tick_bytes);
     }
     const dim3 grid(nsplit, a.nkv, a.M);
     cudaError_t le;
@@ -537,8 +486,8 @@ static cudaError_t attn_noalloc_scratch(float** out) {
     return cudaSuccess;
 }
 
-// Same arithmetic, same context splitting and same kernels as bw_attention_decode_batched_gqa_device, with the
-// partial records in the fixed array.  No partial has to start from zero: every (head, split) record that the
+// Same arithmetic and the same split kernel as bw_attention_decode_batched_gqa_device, with the partial records in
+// the fixed array and a separate merge launch.  No partial has to start from zero: every (head, split) record that the
 // merge kernel reads is written in full by the split kernel of the same call, empty splits included.
 extern "C" int bw_attention_decode_batched_gqa_noalloc(float* output, const float* Q, const float* K_cache,
                                                        const float* V_cache, const int* d_seq_pos, int num_q_heads,
@@ -554,7 +503,8 @@ extern "C" int bw_attention_decode_batched_gqa_noalloc(float* output, const floa
     a.out = output; a.Q = Q; a.K = K_cache; a.V = V_cache; a.d_seq_pos = d_seq_pos; a.per_seq = 0;
     a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
     a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
-    // the split rule of attn_launch, with the whole cache as the context bound
+    // Its own fixed split rule (the allocating entry points size their splits by waves; the merge accepts any
+    // split count): about two CTAs per SM, at least 64 positions per split, at most 64 splits, over the whole cache.
     const int ctx = max_seq_len;
     const int sms = sm_count(current_device());
     int nsplit = (2 * sms + M * a.nkv - 1) / (M * a.nkv);

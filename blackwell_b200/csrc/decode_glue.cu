@@ -49,6 +49,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_kernel(float* q_out, __ha
     if (is_q) {
         *reinterpret_cast<float4*>(q_out + ((size_t)m * nqh + h) * kHeadDim + 4 * lane) = v;
     } else {
+        // A position outside the cache (a sequence that has run past max_seq) is never written.
+        if ((unsigned)pos >= (unsigned)max_seq) return;
         const int kvh = is_k ? h - nqh : h - nqh - nkv;
         __half* dst = (is_k ? k_cache : v_cache) + (size_t)m * kv_batch_elems + kv_layer_elems +
                       ((size_t)kvh * max_seq + pos) * kHeadDim + 4 * lane;
@@ -120,7 +122,7 @@ __device__ __forceinline__ unsigned long long bmax64(unsigned long long v, unsig
 }
 
 __global__ void __launch_bounds__(256) argmax_batched_kernel(const float* logits, long stride, int vocab,
-                                                             int* out_ids, int* seq_pos_to_advance) {
+                                                             int* out_ids, int* seq_pos_to_advance, int pos_limit) {
     __shared__ unsigned long long sh[32];
     __shared__ bool last;
     const int m = blockIdx.y;
@@ -151,7 +153,8 @@ __global__ void __launch_bounds__(256) argmax_batched_kernel(const float* logits
     if (threadIdx.x == 0) {
         out_ids[m] = (int)(0xFFFFFFFFu - (unsigned int)(b2 & 0xFFFFFFFFull));
         g_bargmax_ticket[m] = 0;
-        if (seq_pos_to_advance) seq_pos_to_advance[m] += 1;
+        // positions stop at pos_limit (the last row of the cache), so a replayed step can never index past it
+        if (seq_pos_to_advance && (pos_limit <= 0 || seq_pos_to_advance[m] < pos_limit)) seq_pos_to_advance[m] += 1;
     }
 }
 
@@ -187,14 +190,14 @@ extern "C" int bw_embed_gather_f16(float* x_out, const uint16_t* table_f16, cons
 }
 
 extern "C" int bw_sample_argmax_batched(const float* logits, long row_stride, int vocab, int M, int* out_ids,
-                                        int* seq_pos_to_advance_or_null, void* stream) {
+                                        int* seq_pos_to_advance_or_null, int pos_limit, void* stream) {
     if (!logits || !out_ids || vocab < 1 || M < 1 || M > kBatchArgmaxRows || row_stride < vocab)
         return cudaErrorInvalidValue;
     int blocks = (vocab + 256 * 8 - 1) / (256 * 8);
     if (blocks > kBatchArgmaxBlocks) blocks = kBatchArgmaxBlocks;
     const dim3 grid(blocks, M);
     argmax_batched_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, row_stride, vocab, out_ids,
-                                                                              seq_pos_to_advance_or_null);
+                                                                              seq_pos_to_advance_or_null, pos_limit);
     count_launch(1);
     return cudaPeekAtLastError();
 }

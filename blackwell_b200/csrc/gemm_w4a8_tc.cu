@@ -455,7 +455,7 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
-    if (t == 0 && *abort_flag) atomicExch(&g_status, kStatusMbarTimeout);
+    if (t == 0 && *abort_flag) atomicExch(a.status, kStatusMbarTimeout);
 }
 
 // ----------------------------------------------------------------------------------------------------------
@@ -480,44 +480,15 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-struct TcScratch {
-    unsigned char* ptr = nullptr;
-    size_t bytes = 0;
-};
-static TcScratch g_tc_scratch[kMaxDevices];
-static std::mutex g_tc_mu;
-
-// Grow-only per-device scratch: activation chunks, K-split partials, tickets (kept zero between calls).
-static cudaError_t tc_scratch(size_t bytes, unsigned char** out) {
-    std::lock_guard<std::mutex> lk(g_tc_mu);
-    TcScratch& s = g_tc_scratch[current_device()];
-    if (s.bytes < bytes) {
-        if (s.ptr) cudaFree(s.ptr);
-        s.ptr = nullptr; s.bytes = 0;
-        const size_t want = bytes < ((size_t)16 << 20) ? ((size_t)16 << 20) : bytes;
-        cudaError_t e = cudaMalloc(&s.ptr, want);
-        if (e != cudaSuccess) return e;
-        e = cudaMemset(s.ptr, 0, want);
-        if (e != cudaSuccess) return e;
-        s.bytes = want;
-    }
-    *out = s.ptr;
-    return cudaSuccess;
+// Per-device scratch: activation chunks, K-split partials, tickets (kept zero between calls).
+static GrowScratch g_tc_scratch;
+cudaError_t reserve_scratch(size_t bytes) {
+    unsigned char* p = nullptr;
+    return bytes ? g_tc_scratch.get(bytes, (size_t)16 << 20, nullptr, &p) : cudaSuccess;
 }
 
 static int g_tc_ksplit_override = 0;
 void set_ksplit_override(int v) { g_tc_ksplit_override = v; }
-void set_debug(int) {}  // the stage-skipping switches of the timing ablations are no longer compiled in
-
-int read_clear_status() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) {
-        const int zero = 0;
-        cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
-    }
-    return v;
-}
 
 bool eligible(const GemvArgs& a, int M) {
     if (M < 1 || M > 64 || a.K % 32 != 0 || a.K < 32) return false;
@@ -542,23 +513,43 @@ static cudaError_t launch_n(const CUtensorMap& map_w, const TcArgs& t, int grid,
     return cudaPeekAtLastError();
 }
 
+// Launch geometry and scratch layout of one call: [tickets][activation chunks][K-split partials].
+struct TcLayout {
+    int Mpad, nchunks, tiles, ksplit;
+    size_t xb_off, part_off, part_bytes;
+};
+static TcLayout tc_layout(int M, int N, int K) {
+    TcLayout l;
+    l.Mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    l.nchunks = (K + kKc - 1) / kKc;
+    l.tiles = (N + kRows - 1) / kRows;
+    const int sms = sm_count(current_device());
+    int ksplit = g_tc_ksplit_override > 0 ? g_tc_ksplit_override : sms / l.tiles;  // whole waves of one CTA per SM
+    if (ksplit > l.nchunks) ksplit = l.nchunks;
+    if (ksplit < 1) ksplit = 1;
+    l.ksplit = ksplit;
+    const size_t xb_bytes = (size_t)l.nchunks * xb_chunk_bytes(l.Mpad);
+    l.part_bytes = ksplit > 1 ? (size_t)l.tiles * ksplit * l.Mpad * kRows * sizeof(float) : 0;
+    const size_t ticket_bytes = (size_t)l.tiles * sizeof(unsigned int);
+    l.xb_off = (ticket_bytes + 255) & ~(size_t)255;
+    l.part_off = (l.xb_off + xb_bytes + 255) & ~(size_t)255;
+    return l;
+}
+size_t scratch_bytes(int M, int N, int K) {
+    if (M < 1 || N < 1 || K < 32) return 0;
+    const TcLayout l = tc_layout(M < 64 ? M : 64, N, K);
+    return l.part_off + l.part_bytes;
+}
+
 // y = W . q8(prologue(x)) for 1..64 sequences on the tensor cores.  `a` carries the operands as for the streaming
 // kernel (x kinds int8 / f16 / f32 / f32+norm / swiglu; binary16 weight scales).
 cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st) {
-    const int Mpad = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-    const int nchunks = (a.K + kKc - 1) / kKc;
-    const int tiles = (a.N + kRows - 1) / kRows;
+    const TcLayout lay = tc_layout(M, a.N, a.K);
+    const int Mpad = lay.Mpad, nchunks = lay.nchunks, tiles = lay.tiles, ksplit = lay.ksplit;
     const int sms = sm_count(current_device());
-    int ksplit = g_tc_ksplit_override > 0 ? g_tc_ksplit_override : sms / tiles;  // whole waves of one CTA per SM
-    if (ksplit > nchunks) ksplit = nchunks;
-    if (ksplit < 1) ksplit = 1;
-    const size_t xb_bytes = (size_t)nchunks * xb_chunk_bytes(Mpad);
-    const size_t part_bytes = ksplit > 1 ? (size_t)tiles * ksplit * Mpad * kRows * sizeof(float) : 0;
-    const size_t ticket_bytes = (size_t)tiles * sizeof(unsigned int);
-    const size_t xb_off = (ticket_bytes + 255) & ~(size_t)255;
-    const size_t part_off = (xb_off + xb_bytes + 255) & ~(size_t)255;
+    const size_t xb_off = lay.xb_off, part_off = lay.part_off, part_bytes = lay.part_bytes;
     unsigned char* scratch = nullptr;
-    cudaError_t e = tc_scratch(part_off + part_bytes, &scratch);
+    cudaError_t e = g_tc_scratch.get(part_off + part_bytes, (size_t)16 << 20, st, &scratch);
     if (e != cudaSuccess) return e;
 
     CUtensorMap map_w;
@@ -586,6 +577,7 @@ cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st) {
     t.nkb = a.K / 16;
     t.partial = reinterpret_cast<float*>(scratch + part_off);
     t.tickets = reinterpret_cast<unsigned int*>(scratch);
+    t.status = a.status;
     t.N = a.N; t.M = M; t.Mpad = Mpad; t.nchunks = nchunks; t.ksplit = ksplit; t.map_elem = 4;
     const int grid = tiles * ksplit < sms ? tiles * ksplit : sms;  // persistent: one CTA per SM at most
     if (Mpad == 16) return launch_n<16>(map_w, t, grid, st);

@@ -51,6 +51,7 @@ struct TcArgs {
     int nkb;                  // K / 16
     float* partial;           // [tiles][ksplit][Mpad][128] when ksplit > 1
     unsigned int* tickets;    // [tiles], zero before and after the call
+    int* status;              // device status word
     int N, M, Mpad;           // Mpad = MMA N in {16, 32, 64}
     int nchunks;              // ceil(K / 256)
     int ksplit;               // CTAs sharing one row tile

@@ -14,14 +14,16 @@
 namespace bw {
 
 void set_attn_mma(int v);  // attention_decode.cu
-namespace peer { void set_two_step_min_kb(int kb); }  // peer_allreduce.cu
+cudaError_t attn_reserve_scratch(size_t bytes);
+size_t attn_scratch_bytes(int M, int nqh, int nkv, int ctx);
+namespace peer { void set_two_step_min_kb(int kb); void set_wait_limit_ms(int ms); }  // peer_allreduce.cu
 
 namespace tc {  // tensor-core path, gemm_w4a8_tc.cu
 bool eligible(const GemvArgs& a, int M);
 cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st);
-int read_clear_status();
+cudaError_t reserve_scratch(size_t bytes);
+size_t scratch_bytes(int M, int N, int K);
 void set_ksplit_override(int v);
-void set_debug(int v);
 }  // namespace tc
 
 // --------------------------------------------------------------------------
@@ -127,6 +129,21 @@ static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 static std::atomic<int> g_pdl{1};
 bool pdl_enabled() { return g_pdl.load() != 0; }
+
+// One status word per device for the whole library: kernels that give up on a bounded wait store a code here.
+static __device__ int g_status_word = 0;
+int* status_word_ptr() {
+    static int* ptr[kMaxDevices] = {nullptr};
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    const int dev = current_device();
+    if (!ptr[dev]) {
+        int* p = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word) != cudaSuccess) return nullptr;
+        ptr[dev] = p;
+    }
+    return ptr[dev];
+}
 
 struct StreamPlan {
     bool ok = false;
@@ -274,6 +291,8 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
     if (a.K <= 0 || a.K % 16 != 0 || a.N < 1 || M < 1) return cudaErrorInvalidValue;
     if (!a.y || !a.W || !a.Wsc || !a.x) return cudaErrorInvalidValue;
     if (!aligned(a.W, 8) || !aligned(a.x, 8)) return cudaErrorInvalidValue;
+    a.status = status_word_ptr();
+    if (!a.status) return cudaErrorInitializationError;
     const bool prequant = (a.xkind == kXInt8 || a.xkind == kXInt4);
     a.nch = a.K / 32;
     if (a.x_stride <= 0) a.x_stride = a.K;
@@ -421,17 +440,28 @@ extern "C" int bw_gemv_block_dots(int32_t* dots, const void* x, int a8, const ui
 }
 
 extern "C" int bw_device_status(int* status_out) {
+    int* p = status_word_ptr();
+    if (!p) return cudaErrorInitializationError;
     int v = 0;
-    cudaError_t e = cudaMemcpyFromSymbol(&v, g_status, sizeof(int));
+    cudaError_t e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return e;
     if (v != 0) {
         const int zero = 0;
-        e = cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+        e = cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
     }
-    const int v2 = tc::read_clear_status();
-    if (v == 0 && v2 > 0) v = v2;
     if (status_out) *status_out = v;
     return e;
+}
+
+extern "C" size_t bw_gemv_scratch_bytes(int M, int N, int K) { return tc::scratch_bytes(M, N, K); }
+extern "C" size_t bw_attention_scratch_bytes(int M, int num_q_heads, int num_kv_heads, int max_context) {
+    return attn_scratch_bytes(M, num_q_heads, num_kv_heads, max_context);
+}
+
+extern "C" int bw_reserve_scratch(size_t gemv_bytes, size_t attention_bytes) {
+    cudaError_t e = tc::reserve_scratch(gemv_bytes);
+    if (e != cudaSuccess) return e;
+    return attn_reserve_scratch(attention_bytes);
 }
 
 extern "C" int bw_set_tuning(int key, int value) {
@@ -443,10 +473,10 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 4: g_tune_threads = value; return 0;
         case 5: g_tune_tc_min = value; return 0;
         case 6: tc::set_ksplit_override(value); return 0;
-        case 7: tc::set_debug(value); return 0;
         case 8: g_pdl = value; return 0;
         case 9: set_attn_mma(value); return 0;
         case 10: peer::set_two_step_min_kb(value); return 0;
+        case 11: peer::set_wait_limit_ms(value); return 0;
         default: return cudaErrorInvalidValue;
     }
 }

@@ -37,9 +37,6 @@ enum XKind : int {
     kXSwigluI4 = 8,    // SwiGLU then int4 quantize
 };
 
-// Device status word of this translation unit (see bw_device_status).
-static __device__ int g_status = 0;
-
 struct XChunk {      // one 32-element activation chunk of one sequence
     uint32_t e[4];   // even-k bytes of weight word i
     uint32_t o[4];   // odd-k bytes of weight word i
@@ -55,6 +52,7 @@ struct GemvArgs {
     const float* xsc;       // [M][K/16] for the pre-quantized kinds
     const float* norm_w;    // [K] for kXFloatNorm
     const float* residual;  // optional [M][y_stride]: added to the result (may alias y)
+    int* status;            // device status word (bw_device_status)
     long x_stride;          // elements between sequences of x / x2 (f16 and f32 kinds)
     long y_stride;          // elements between sequences of y and residual
     float eps;
@@ -448,7 +446,7 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         for (int s = 0; s < S; ++s) {
             (void)mbar_wait(smem_u32(&bars[s]), 0);
         }
-        atomicExch(&g_status, kStatusMbarTimeout);
+        atomicExch(a.status, kStatusMbarTimeout);
     }
 }
 

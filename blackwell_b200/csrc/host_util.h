@@ -2,6 +2,9 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <mutex>
+#include <vector>
+
 namespace bw {
 
 constexpr int kMaxDevices = 16;
@@ -45,5 +48,45 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 
 // Launch accounting (bw_launch_count).
 void count_launch(int n);
+
+// Device address of the library's status word on the current device (see bw_device_status); nullptr on failure.
+int* status_word_ptr();
+
+// Grow-only per-device scratch memory of one kernel family, zero-filled when allocated.  A block that has been
+// handed out is never freed while the library is loaded: kernel launches already enqueued -- or captured in a CUDA
+// graph -- keep pointing at it, so growth parks the old block instead of freeing it.  Growth allocates (and
+// synchronises), so it cannot happen while the calling stream is being captured: such a call fails with
+// cudaErrorStreamCaptureUnsupported and the caller must size the scratch beforehand (bw_reserve_scratch, or one
+// eager call of the same shape).  All streams of a device share the block: two calls that use it must not overlap.
+class GrowScratch {
+public:
+    cudaError_t get(size_t bytes, size_t floor_bytes, cudaStream_t st, unsigned char** out) {
+        std::lock_guard<std::mutex> lk(mu_);
+        Block& b = cur_[current_device()];
+        if (b.bytes < bytes) {
+            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone)
+                return cudaErrorStreamCaptureUnsupported;
+            size_t want = bytes < floor_bytes ? floor_bytes : bytes;
+            if (want < 2 * b.bytes) want = 2 * b.bytes;  // geometric growth bounds what the parked blocks hold
+            unsigned char* p = nullptr;
+            cudaError_t e = cudaMalloc(&p, want);
+            if (e != cudaSuccess) return e;
+            e = cudaMemset(p, 0, want);  // arrival counters inside must start at zero
+            if (e != cudaSuccess) { cudaFree(p); return e; }
+            if (b.ptr) retired_.push_back(b.ptr);
+            b.ptr = p;
+            b.bytes = want;
+        }
+        *out = b.ptr;
+        return cudaSuccess;
+    }
+
+private:
+    struct Block { unsigned char* ptr = nullptr; size_t bytes = 0; };
+    Block cur_[kMaxDevices];
+    std::vector<unsigned char*> retired_;
+    std::mutex mu_;
+};
 
 }  // namespace bw

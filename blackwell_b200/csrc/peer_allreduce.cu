@@ -7,7 +7,8 @@
 // processes, or direct peer access inside one process).  The GEMV writes its partial sums straight into the local
 // slot; one kernel then
 //   1. tells every peer "my slot is complete" (a release store of the call's epoch into the peer's flag array),
-//   2. waits for the same word from every peer (acquire loads, bounded: gives up after ~2 s and sets the status),
+//   2. waits for the same word from every peer (acquire loads, bounded: gives up after ~2 s -- or the limit set
+//      through bw_set_tuning key 11 -- sets the status word to 3, leaves the output untouched and returns),
 //   3. sums the slot of every rank, in rank order, with plain 16-byte peer loads, adds an optional residual, and
 //      writes the result to local memory.  All ranks add in the same order, so they hold bit-identical results.
 // Slots alternate between consecutive exchanges: a rank overwrites a slot only after it finished the following
@@ -45,6 +46,9 @@ static_assert(kStatusOff + sizeof(int) <= kHeaderBytes, "header too small");
 // Smallest vector (KiB) that takes the two-step form on four or more ranks; 0 = the default.
 static int g_two_step_min_kb = 0;
 void set_two_step_min_kb(int kb) { g_two_step_min_kb = kb; }
+// Longest time a CTA waits for a peer's flag, in milliseconds; 0 = the default of about two seconds.
+static int g_wait_limit_ms = 0;
+void set_wait_limit_ms(int ms) { g_wait_limit_ms = ms; }
 
 struct Comm {
     int world, rank, device;
@@ -63,6 +67,7 @@ struct Args {
     int* status;
     int world, rank;
     unsigned long long n4;            // number of float4
+    long long wait_cycles;            // a wait for a peer gives up after this many SM clock cycles
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -94,6 +99,17 @@ __device__ __forceinline__ float4 sum_ranks(const Args& a, unsigned long long i)
     return s;
 }
 
+// Bounded wait of thread t < world for peer t's word in this rank's flag array; false when it gave up.
+__device__ __forceinline__ bool wait_peer_flag(const uint32_t* mine, uint32_t e, long long limit) {
+    const long long t0 = clock64();
+#pragma unroll 1
+    while (true) {
+        if ((int)(ld_acquire_sys(mine) - e) >= 0) return true;
+        if (clock64() - t0 > limit) return false;
+        __nanosleep(20);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const Args a) {
     __shared__ uint32_t s_epoch;
     __shared__ int s_fail;
@@ -111,16 +127,7 @@ __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const Args a) 
     const uint32_t e = s_epoch;
     if (t < a.world) {
         st_release_sys(a.flags[t] + c * kMaxWorld + a.rank, e);            // to peer t: rank's slot is complete
-        const uint32_t* mine = a.flags[a.rank] + c * kMaxWorld + t;        // from peer t
-        const long long t0 = clock64();
-        bool ok = false;
-#pragma unroll 1
-        while (true) {
-            if ((int)(ld_acquire_sys(mine) - e) >= 0) { ok = true; break; }
-            if (clock64() - t0 > 4000000000ll) break;                       // ~2 s at any SM clock
-            __nanosleep(20);
-        }
-        if (!ok) s_fail = 1;
+        if (!wait_peer_flag(a.flags[a.rank] + c * kMaxWorld + t, e, a.wait_cycles)) s_fail = 1;   // from peer t
     }
     __syncthreads();
     if (s_fail) {
@@ -136,17 +143,6 @@ __global__ void __launch_bounds__(kThreads) peer_allreduce_kernel(const Args a) 
     if (t == 0) a.epochs[c] = e;
 }
 
-
-// Bounded wait of thread t < world for peer t's word in this rank's flag array; false when it gave up.
-__device__ __forceinline__ bool wait_peer_flag(const uint32_t* mine, uint32_t e) {
-    const long long t0 = clock64();
-#pragma unroll 1
-    while (true) {
-        if ((int)(ld_acquire_sys(mine) - e) >= 0) return true;
-        if (clock64() - t0 > 4000000000ll) return false;                    // ~2 s at any SM clock
-        __nanosleep(20);
-    }
-}
 
 // Two-step form.  The vector is cut into world slices of slice4 float4 (the last may be short); CTA c of rank r sums
 // the float4 [c * per_cta, (c + 1) * per_cta) of slice r and stores them to every rank; after the second barrier CTA c
@@ -166,7 +162,7 @@ __global__ void __launch_bounds__(kThreads) peer_allreduce2_kernel(const Args a,
     const uint32_t e = s_epoch;
     if (t < a.world) {
         st_release_sys(a.flags[t] + c * kMaxWorld + a.rank, e);
-        if (!wait_peer_flag(a.flags[a.rank] + c * kMaxWorld + t, e)) s_fail = 1;
+        if (!wait_peer_flag(a.flags[a.rank] + c * kMaxWorld + t, e, a.wait_cycles)) s_fail = 1;
     }
     __syncthreads();
     const bool fail1 = s_fail != 0;
@@ -190,7 +186,7 @@ __global__ void __launch_bounds__(kThreads) peer_allreduce2_kernel(const Args a,
         f2 = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(a.flags[t]) + kFlag2Off);
         st_release_sys(f2 + c * kMaxWorld + a.rank, e);
         const uint32_t* mine2 = reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(a.flags[a.rank]) + kFlag2Off);
-        if (!wait_peer_flag(mine2 + c * kMaxWorld + t, e)) s_fail = 1;
+        if (!wait_peer_flag(mine2 + c * kMaxWorld + t, e, a.wait_cycles)) s_fail = 1;
     }
     __syncthreads();
     if (s_fail) {
@@ -265,17 +261,19 @@ extern "C" int bw_peer_comm_attach(void* comm, int peer_rank, void* peer_comm_sa
     if (!cm || !pc || peer_rank < 0 || peer_rank >= cm->world || peer_rank == cm->rank || pc->rank != peer_rank ||
         pc->slot_bytes != cm->slot_bytes || cm->base[peer_rank])
         return cudaErrorInvalidValue;
-    int can = 0;
-    cudaError_t e = cudaDeviceCanAccessPeer(&can, cm->device, pc->device);
-    if (e != cudaSuccess) return e;
-    if (!can) return cudaErrorPeerAccessUnsupported;
-    int prev = 0;
-    cudaGetDevice(&prev);
-    cudaSetDevice(cm->device);
-    e = cudaDeviceEnablePeerAccess(pc->device, 0);
-    if (e == cudaErrorPeerAccessAlreadyEnabled) { e = cudaSuccess; cudaGetLastError(); }
-    cudaSetDevice(prev);
-    if (e != cudaSuccess) return e;
+    if (cm->device != pc->device) {  // two communicators on one device see each other's memory as it is
+        int can = 0;
+        cudaError_t e = cudaDeviceCanAccessPeer(&can, cm->device, pc->device);
+        if (e != cudaSuccess) return e;
+        if (!can) return cudaErrorPeerAccessUnsupported;
+        int prev = 0;
+        cudaGetDevice(&prev);
+        cudaSetDevice(cm->device);
+        e = cudaDeviceEnablePeerAccess(pc->device, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) { e = cudaSuccess; cudaGetLastError(); }
+        cudaSetDevice(prev);
+        if (e != cudaSuccess) return e;
+    }
     cm->base[peer_rank] = pc->base[pc->rank];
     return cudaSuccess;
 }
@@ -303,6 +301,8 @@ extern "C" int bw_peer_allreduce_f32(void* comm, int slot, float* out, const flo
     a.epochs = reinterpret_cast<uint32_t*>(mine + kEpochOff);
     a.status = reinterpret_cast<int*>(mine + kStatusOff);
     a.out = out; a.residual = residual_or_null; a.world = cm->world; a.rank = cm->rank; a.n4 = n / 4;
+    // counted on the SM clock (at most ~2.1 GHz): the default is about two seconds at any clock
+    a.wait_cycles = g_wait_limit_ms > 0 ? (long long)g_wait_limit_ms * 2100000ll : 4000000000ll;
     for (int r = 0; r < cm->world; ++r)
         a.result[r] = reinterpret_cast<float*>(cm->base[r] + kHeaderBytes + 2 * cm->slot_bytes);
     const int cap = sm_count(cm->device) < kMaxCtas ? sm_count(cm->device) : kMaxCtas;

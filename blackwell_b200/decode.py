@@ -177,7 +177,7 @@ class DecodeEngine:
         k.gemv_w4a8_decode(self.logits, 0, None, self.x, None, 0, self.rn_final, eps, self.lm[0], self.lm[1], H,
                            self.v_local, M)
         if self.world == 1:
-            k.sample_argmax_batched(self.logits, self.v_local, self.v_local, M, self.tokens, self.pos)
+            k.sample_argmax_batched(self.logits, self.v_local, self.v_local, M, self.tokens, self.pos, self.max_seq - 1)
         else:
             self._tp_argmax()
 
@@ -188,7 +188,7 @@ class DecodeEngine:
         M = self.M
         loc = torch.empty((M,), dtype=torch.int32, device=self.dev) if not hasattr(self, "_loc") else self._loc
         self._loc = loc
-        k.sample_argmax_batched(self.logits, self.v_local, self.v_local, M, loc, self.pos)
+        k.sample_argmax_batched(self.logits, self.v_local, self.v_local, M, loc, self.pos, self.max_seq - 1)
         idx = loc.long()
         self.cand[:, 0] = self.logits.gather(1, idx[:, None])[:, 0]
         self.cand[:, 1] = (idx + self.v0).float()

@@ -234,6 +234,7 @@ def embed_gather_f16(x_out, table_f16, d_tokens, H, vocab, M, stream=None):
     _chk("embed_gather_f16", _L.bw_embed_gather_f16(_p(x_out), _p(table_f16), _p(d_tokens), H, vocab, M, _s(stream)))
 
 
-def sample_argmax_batched(logits, row_stride, vocab, M, out_ids, seq_pos_to_advance=None, stream=None):
+def sample_argmax_batched(logits, row_stride, vocab, M, out_ids, seq_pos_to_advance=None, pos_limit=0, stream=None):
     _chk("sample_argmax_batched", _L.bw_sample_argmax_batched(_p(logits), C.c_long(row_stride), vocab, M,
-                                                              _p(out_ids), _p(seq_pos_to_advance), _s(stream)))
+                                                              _p(out_ids), _p(seq_pos_to_advance), int(pos_limit),
+                                                              _s(stream)))

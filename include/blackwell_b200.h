@@ -169,9 +169,11 @@ int bw_embed_gather_f16(float* x_out, const uint16_t* table_f16, const int* d_to
                         void* stream);
 /* Greedy argmax of each row of logits f32 [M][row_stride] (rule of sample_argmax_gpu,
  * src/kernels/sample_gpu.cu:30-60) into out_ids[M]; when seq_pos_to_advance is not NULL each of its M entries
- * is incremented, which closes a decode step inside a CUDA graph.  M <= 256. */
+ * is incremented, which closes a decode step inside a CUDA graph -- but never beyond pos_limit (pass
+ * max_seq_len - 1; <= 0 means no limit), so that a replayed graph cannot push a position past the end of the
+ * KV cache.  M <= 256. */
 int bw_sample_argmax_batched(const float* logits, long row_stride, int vocab, int M, int* out_ids,
-                             int* seq_pos_to_advance_or_null, void* stream);
+                             int* seq_pos_to_advance_or_null, int pos_limit, void* stream);
 
 /* Attention for callers that must not allocate.  No counterpart in the reference: it exists for hosts
  * that cannot reach the CUDA allocator once they are serving -- a process that has given all device memory
@@ -240,7 +242,7 @@ int bw_f32_file_read(const char* path, float* data_out, size_t n);
  * bw_peer_comm_create allocates this rank's region on the current device (two slots of slot_bytes; the GEMV writes
  * its partial sums into bw_peer_comm_slot(comm, slot) directly).  Between processes the 64-byte handle from
  * bw_peer_comm_handle is passed to every peer's bw_peer_comm_open; inside one process bw_peer_comm_attach links two
- * communicators instead.  bw_peer_allreduce_f32 (n % 4 == 0, n * 4 <= slot_bytes, 16-byte aligned out/residual)
+ * communicators instead (on two devices with peer access, or on one and the same device).  bw_peer_allreduce_f32 (n % 4 == 0, n * 4 <= slot_bytes, 16-byte aligned out/residual)
  * enqueues one kernel: signal, bounded wait (~2 s, then status 3 from bw_peer_comm_status and no result), sum of
  * every rank's slot in rank order (+ residual) into out.  Every rank must issue the same sequence of calls with
  * alternating slot (0, 1, 0, ...); creation and teardown synchronise the device, the all-reduce itself allocates
@@ -254,13 +256,28 @@ int bw_peer_allreduce_f32(void* comm, int slot, float* out, const float* residua
 int bw_peer_comm_status(void* comm, int* status_out);
 int bw_peer_comm_destroy(void* comm);
 
+/* Library-owned scratch memory.  Two kernel families keep a per-device, grow-only scratch block: the tensor-core
+ * GEMV (batches of 8 sequences and more through bw_gemv_w4a8*: prepared activations, K-split partial sums, arrival
+ * counters) and the allocating attention entry points (split partials, arrival counters).  A block is shared by all
+ * streams of the device -- two calls of the same family must not overlap on one GPU -- and grows (cudaMalloc +
+ * cudaMemset, synchronising) when a larger problem arrives; an outgrown block stays allocated until the library is
+ * unloaded, because launches already enqueued or captured in a CUDA graph still point at it.  A call that would
+ * have to grow while its stream is being captured fails with cudaErrorStreamCaptureUnsupported.  To keep the
+ * serving path free of allocations, reserve the largest sizes once at start-up: bw_gemv_scratch_bytes /
+ * bw_attention_scratch_bytes give upper bounds for a shape (take the maximum over the shapes in use).  No
+ * counterpart in the reference, whose kernels need no scratch. */
+size_t bw_gemv_scratch_bytes(int M, int N, int K);
+size_t bw_attention_scratch_bytes(int M, int num_q_heads, int num_kv_heads, int max_context);
+int bw_reserve_scratch(size_t gemv_bytes, size_t attention_bytes);
+
 /* Tuning knobs for experiments: key 0 = ring stages (0 = automatic),
  * key 1 = CTAs per SM cap (0 = automatic), key 2 = force the plain-load kernel,
  * key 3 = rows per thread group and tile cap, key 4 = threads per CTA target,
  * key 5 = smallest batch sent to the tensor-core kernel (0 = default 8), key 6 = its K-split (0 = automatic),
- * key 7 = unused (accepted, no effect), key 8 = programmatic dependent launch on (1, default) / off (0), key 9 = tensor-core attention kernel
+ * key 8 = programmatic dependent launch on (1, default) / off (0), key 9 = tensor-core attention kernel
  * for the binary16 cache on (1, default) / off (0: scalar kernel, for comparison runs), key 10 = smallest vector in
- * KiB that the peer all-reduce sums in two steps on four or more ranks (0 = default 4096). */
+ * KiB that the peer all-reduce sums in two steps on four or more ranks (0 = default 4096), key 11 = longest wait of
+ * the peer all-reduce for another rank in milliseconds (0 = default, about 2000). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);

@@ -162,6 +162,49 @@ def test_qk_norm_rope_kv_and_embed_and_batched_argmax(cuda):
     assert np.array_equal(p.cpu().numpy(), pos + 2)
 
 
+def test_positions_outside_the_cache_are_never_written(cuda):
+    """A sequence whose position has reached max_seq (a replayed step that ran past the cache) must leave the cache
+    and everything behind it alone, and the batched argmax must stop advancing positions at its limit."""
+    import torch
+
+    from blackwell_b200 import kernels as k
+
+    M, nq, nkv, max_seq = 3, 4, 2, 16
+    g = synth.rng(420)
+    qkv = g.normal(size=(M, (nq + 2 * nkv) * 128)).astype(np.float32)
+    qn, kn = synth.norm_weight(128, 421), synth.norm_weight(128, 422)
+    kv_layer = nkv * max_seq * 128
+    canary = 4096
+    # one allocation: [K cache][canary]; the last sequence's last head ends where the canary begins
+    buf_k = torch.full((M * kv_layer + canary,), 7.0, dtype=torch.float16, device="cuda")
+    buf_v = torch.full((M * kv_layer + canary,), 7.0, dtype=torch.float16, device="cuda")
+    q = torch.empty((M, nq * 128), dtype=torch.float32, device="cuda")
+    pos = np.array([3, max_seq, max_seq + 5], np.int32)
+    k.qk_norm_rope_kv_f16(q, buf_k, buf_v, to_dev(qkv), to_dev(qn), to_dev(kn), to_dev(pos), nq, nkv, 128, max_seq, M,
+                          kv_layer, 0, 1e-6, 1e6)
+    torch.cuda.synchronize()
+    for buf in (buf_k, buf_v):
+        h = buf.cpu().numpy()
+        cache = h[:M * kv_layer].reshape(M, nkv, max_seq, 128)
+        assert (h[M * kv_layer:] == 7.0).all()                 # nothing behind the cache
+        assert (cache[1:] == 7.0).all()                        # the two out-of-range sequences wrote nothing
+        assert (cache[0, :, 3] != 7.0).any() and (np.delete(cache[0], 3, axis=1) == 7.0).all()
+    # the fp32 reference-format update with a device position outside the cache
+    kc = torch.full((nkv * max_seq * 128 + canary,), 7.0, dtype=torch.float32, device="cuda")
+    vc = kc.clone()
+    new = to_dev(g.normal(size=nkv * 128).astype(np.float32))
+    k.update_kv_cache_device(kc, vc, new, new, 0, to_dev(np.array([max_seq], np.int32)), nkv, 128, max_seq)
+    torch.cuda.synchronize()
+    assert (kc == 7.0).all() and (vc == 7.0).all()
+    # positions stop at the limit
+    logits = to_dev(g.normal(size=(M, 1000)).astype(np.float32))
+    ids = torch.zeros(M, dtype=torch.int32, device="cuda")
+    p = to_dev(np.array([3, max_seq - 2, max_seq - 1], np.int32))
+    for _ in range(3):
+        k.sample_argmax_batched(logits, 1000, 1000, M, ids, p, max_seq - 1)
+    assert p.cpu().tolist() == [6, max_seq - 1, max_seq - 1]
+
+
 def test_gemv_decode_entry_residual_and_strides(cuda):
     import torch
 

@@ -241,6 +241,25 @@ def test_attention_matches_reference_cuda_short_context(k):
     print("reference attention vs oracle:", max_abs_rel(b.cpu().numpy(), ref))
 
 
+@pytest.mark.parametrize("nqh,nkv", [(32, 8), (4, 2)])
+def test_attention_f16_cache_context_longer_than_the_hint(k, nqh, nkv):
+    """The context hint only sizes the splits: sequences that have grown well past it (a captured step replayed many
+    times) must still attend to every position (tensor-core kernel: 4 heads per kv head; scalar kernel: 2)."""
+    import torch
+
+    M, hd, max_seq, hint = 3, 128, 1024, 200
+    g = synth.rng(230)
+    Q = g.normal(size=(M, nqh * hd)).astype(np.float32)
+    Kc = synth.kv_cache_f16((M, nkv, max_seq, hd), 231)
+    Vc = synth.kv_cache_f16((M, nkv, max_seq, hd), 232)
+    pos = np.array([150, 777, 1023], np.int32)
+    out = torch.empty((M, nqh * hd), dtype=torch.float32, device="cuda")
+    k.attention_decode_f16kv(out, to_dev(Q), to_dev(Kc.view(np.uint16)), to_dev(Vc.view(np.uint16)), to_dev(pos),
+                             hint, nqh, nkv, hd, max_seq, M, nkv * max_seq * hd, 0)
+    ref = oracle.attention_decode_f16kv(Q, Kc, Vc, pos, nqh, nkv, hd, max_seq, M)
+    assert max_abs_rel(out.cpu().numpy(), ref) < 1e-4
+
+
 @pytest.mark.parametrize("M,nqh,nkv,max_seq,ctx", [(1, 32, 8, 2048, 2048), (8, 32, 8, 2048, 2048),
                                                     (4, 64, 8, 4096, 4096), (2, 32, 8, 300, 131)])
 def test_attention_decode_f16_cache_per_sequence_positions(k, M, nqh, nkv, max_seq, ctx):
