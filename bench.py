@@ -35,9 +35,12 @@ from blackwell_b200 import shapes  # noqa: E402
 METRIC = "int4_gemv_hbm_gbs"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel, per launch, from the ncu capture
-# summarised under profiles/ (None until captured).
-NCU_TRAFFIC_RATIO = 1.023  # (dram read + write) / algorithmic bytes of one launch, profiles/gemv_w4_stream_m1_lmhead65536x4096.md
+FALLBACK_BF16_TFLOPS = 1590.0
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of one launch of the dominant kernel, from one
+# ncu capture of a 65,536-row slice of the LM head (DRAM traffic of this kernel grows in proportion to the rows).
+NCU_TRAFFIC_RATIO = 1.023
+DTYPE = "int8 x int4 -> int32, f16 weight scale / f32 activation scale"
+MIN_TIMED_SECONDS = 0.3  # the timed region lasts at least this long whatever --steps is (clock samples need time)
 
 
 def measured_peak():
@@ -47,6 +50,26 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def int8_tensor_peak_tops():
+    """Dense int8 tensor-core peak used for the M >= 16 rows: twice the measured dense bf16 burst throughput (the
+    int8 rate of the part is twice its bf16 rate; the driver measures bf16 only)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return 2.0 * float(json.load(f)["bf16_tflops"]), "2 x measured bf16"
+    except Exception:
+        return 2.0 * FALLBACK_BF16_TFLOPS, "2 x fallback bf16"
+
+
+def workload_config(world: int):
+    """The `config` object, identical in both arms."""
+    mats = gemv_set()
+    return {"workload": "qwen3-8b-shape per-layer GEMV set, M=1, W4A8 block-16 (configs[1])",
+            "matrices": [[n, N, K] for n, N, K in mats], "bytes_per_step": set_bytes(mats, 1),
+            "l2": "inputs larger than L2 (498 MB set, 126 MB L2)",
+            "parallelism": "tp%d" % world if world > 1 else "single"}
 
 
 _ONLY = None  # (name, N override or None): restricts the set to one matrix, for profiling runs
@@ -151,6 +174,14 @@ def cpu_sample_baseline(threads: int = 0, frac: int = 8, reps: int = 1, seed: in
     return gbs, used, sample, dt
 
 
+def cpu_baseline_record(frac_all: int = 8, frac_one: int = 64):
+    """All-core and single-thread figures of the host port (the single-thread run takes a smaller row sample)."""
+    g, cores, sample, _ = cpu_sample_baseline(0, frac_all, 2)
+    g1, _, sample1, _ = cpu_sample_baseline(1, frac_one, 1)
+    return {"value": g, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+            "single_thread": {"value": g1, "unit": UNIT, "cores": 1, "sample": sample1}}
+
+
 def run_reference(args, rank):
     """Reference arm: the reference has no CPU implementation of this path, so its arithmetic restated on the host
     (oracle/oracle.c, scalar fp32 dequant-dot, OpenMP over rows) is timed on all host cores."""
@@ -172,7 +203,7 @@ def run_reference(args, rank):
         import torch
 
         if torch.cuda.is_available():
-            ref_gpu = per_matrix_times(torch.device("cuda", 0), 1, reference_arm=True)
+            ref_gpu = {"M%d" % mb: per_matrix_times(torch.device("cuda", 0), mb, reference_arm=True) for mb in (1, 8, 16)}
     except Exception as exc:
         ref_gpu = {"error": repr(exc)[:200]}
     t = float(np.mean(times))
@@ -180,9 +211,8 @@ def run_reference(args, rank):
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "int8xint4->int32, fp32 scale", "data": "synthetic",
-        "config": {"workload": "qwen3-8b-shape per-layer GEMV set, M=1, W4A8 block-16 (configs[1])",
-                   "matrices": [[n, N, K] for n, N, K in mats]},
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": workload_config(args.gpus),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -258,16 +288,31 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(3):
         run_step()
     barrier()
+    # A step is one pass over the five matrices.  So that the timed region lasts long enough for the clock sampler
+    # (and for the driver's own samples) whatever --steps is, every one of the K timed steps is measured as the mean
+    # of `passes` back-to-back passes: the timed region holds K x passes passes and ms_per_step = time / (K x passes).
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    for _ in range(10):
+        run_step()
+    p1.record()
+    torch.cuda.synchronize()
+    est = max(p0.elapsed_time(p1) / 10 / 1e3, 1e-6)
+    passes = max(1, int(np.ceil(MIN_TIMED_SECONDS / (est * args.steps))))
+    if world > 1:
+        pt = torch.tensor([passes], dtype=torch.int64, device=dev)
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        passes = int(pt.item())
     sampler = ClockSampler(local_rank)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(args.steps * passes):
         run_step()
     e1.record()
     barrier()
-    launches = launches_per_step * args.steps
+    launches = launches_per_step * args.steps * passes
     clocks = sampler.stop()
     ms = e0.elapsed_time(e1)
     if world > 1:
@@ -275,8 +320,9 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         ms = float(tmax.item())
     assert k.device_status() == 0, "a kernel reported a bounded-wait timeout"
+    assert coll is None or coll.peer is None or coll.peer.status() == 0, "a peer all-reduce gave up waiting for a rank"
     total_bytes = set_bytes(mats, M)  # whole job: the full matrices, whatever the sharding
-    sec_per_step = ms / 1e3 / args.steps
+    sec_per_step = ms / 1e3 / (args.steps * passes)
     value = total_bytes / sec_per_step / 1e9
 
     # ---- end to end through the public call with host buffers (pinned), copies inside the timed region
@@ -323,24 +369,33 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(3):
         e2e_step()
     barrier()
+    e2e_n = args.steps * passes
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(e2e_n):
         e2e_step()
     barrier()
-    e2e_sec = (time.perf_counter() - t0) / args.steps
+    e2e_sec = (time.perf_counter() - t0) / e2e_n
     if world > 1:
         tmax = torch.tensor([e2e_sec], dtype=torch.float64, device=dev)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         e2e_sec = float(tmax.item())
     e2e_val = total_bytes / e2e_sec / 1e9
 
-    # ---- every matrix on its own, L2-cold, beside the reference's own CUDA kernel (rank 0, single GPU)
-    per = []
+    # ---- every matrix on its own, L2-cold (rank 0, single GPU); the reference arm prints the reference's own CUDA
+    # kernels on the same shapes
+    per, per_batched, cfg0 = [], {}, None
     if rank == 0 and world == 1 and not args.only:
         try:
             per = per_matrix_times(dev, M)
+            if M == 1:
+                for mb in (8, 16):
+                    per_batched["M%d" % mb] = per_matrix_times(dev, mb)
         except Exception as exc:
             per = [{"error": repr(exc)[:200]}]
+        try:
+            cfg0 = config0_record(dev)
+        except Exception as exc:
+            cfg0 = {"error": repr(exc)[:200]}
     # ---- configs[2]: the same five matrices at 2..64 sequences per call (graph replay of the set, 1 GPU)
     sweep = []
     if rank == 0 and world == 1 and not args.only and M == 1:
@@ -348,6 +403,13 @@ def run_ours(args, rank, world, local_rank):
             sweep = batch_sweep(dev, state, mats)
         except Exception as exc:
             sweep = [{"error": repr(exc)[:200]}]
+    # ---- N > 1: the values behind the scaling curve -- a small tensor-parallel decode step against the single-GPU one
+    tp_par = None
+    if world > 1 and not args.only:
+        try:
+            tp_par = tp_parity(dev, world, rank)
+        except Exception as exc:
+            tp_par = {"error": repr(exc)[:300]}
     if world > 1:
         barrier()
 
@@ -374,28 +436,31 @@ def run_ours(args, rank, world, local_rank):
     per_launch_bytes = total_bytes / world / max(n_launch, 1)
     per_launch_s = sec_per_step / max(n_launch, 1)
     achieved = per_launch_bytes / per_launch_s / 1e9
-    cpu = None
-    if world == 1:
-        g, cores, sample, _ = cpu_sample_baseline(0, 8, 2)
-        cpu = {"value": g, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    cpu = cpu_baseline_record() if world == 1 else None
+    cfg = workload_config(world)
+    cfg["bytes_per_step"] = total_bytes
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "int8xint4->int32, fp32 scale", "data": "synthetic",
-        "config": {"workload": "qwen3-8b-shape per-layer GEMV set, M=1, W4A8 block-16 (configs[1])",
-                   "matrices": [[n, N, K] for n, N, K in mats], "bytes_per_step": total_bytes,
-                   "l2": "inputs larger than L2 (498 MB set, 126 MB L2)",
-                   "parallelism": "tp%d" % world if world > 1 else "single",
-                   "launch": "cuda graph replay, one step per graph" if use_graph else "host launches"},
-        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": cfg,
+        "launch": "cuda graph replay, one pass per graph" if use_graph else "host launches",
+        "passes_per_step": passes, "timed_region_s": ms / 1e3,
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "schedule": "the caller's (this bench's), not the library's: all inputs go up first, the largest "
+                            "matrix (LM head) is launched first and each result is copied back on a second stream "
+                            "while the next matrix runs; the host synchronises once per pass"},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": int(per_launch_bytes * NCU_TRAFFIC_RATIO), "traffic_note": "ncu capture of a 65536-row slice, scaled by rows", "peak_kind": peak_kind,
-                     "kernel": "gemv_w4_stream_kernel<1,half>", "nominal_frac": achieved / 8000.0},
+                     "kernel": "w4_stream_kernel<1,half>", "nominal_frac": achieved / 8000.0},
         "cpu_baseline": cpu,
+        "config0": cfg0,
         "per_matrix": per,
+        "per_matrix_batched": per_batched,
         "batch_sweep": sweep,
+        "tp_parity": tp_par,
         "decode": decode,
     }
     print(json.dumps(line), flush=True)
@@ -512,9 +577,123 @@ def batch_sweep(dev, state, mats):
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) / reps * 1e3
         nbytes = set_bytes(mats, m)
-        out.append({"M": m, "us_per_step": round(us, 1), "gbs": round(nbytes / us / 1e3, 1),
-                    "roofline_frac": round(nbytes / us / 1e3 / peak, 3), "status": k.device_status()})
+        rec = {"M": m, "us_per_step": round(us, 1), "gbs": round(nbytes / us / 1e3, 1),
+               "roofline_frac": round(nbytes / us / 1e3 / peak, 3), "status": k.device_status()}
+        if m >= 16:  # also against the dense int8 tensor-core roofline (2 M N K integer operations)
+            tpeak, tkind = int8_tensor_peak_tops()
+            tops = sum(2.0 * m * N * K for _, N, K in mats) / us / 1e6
+            rec.update({"int8_tops": round(tops, 2), "tensor_roofline_frac": round(tops / tpeak, 5),
+                        "tensor_peak_tops": tpeak, "tensor_peak_kind": tkind})
+        out.append(rec)
         del g, xs, ys
+    return out
+
+
+def config0_record(dev):
+    """BASELINE.json configs[0] as its own record: one 4096 x 4096 GEMV at M = 1 in the W4A8 format (fp16 activations
+    quantized to int8 by the reference's rule), L2-cold graph replay over 30 weight copies; parity of the same launch
+    against the CPU oracle (outputs against the float64 dequant-dot, per-block int32 dots bit for bit); and the host
+    port's time for the same call, single-thread and all cores."""
+    import torch
+
+    import oracle
+    from blackwell_b200 import kernels as k
+    from blackwell_b200 import synth
+
+    N = K = 4096
+    peak, kind = measured_peak()
+    ncopy = 30
+    Ws = [synth.int4_weights_device(N, K, 9100 + c, device=dev) for c in range(ncopy)]
+    x16 = synth.activations_f16_device(1, K, 9099, device=dev)
+    y = torch.empty((1, N), dtype=torch.float32, device=dev)
+    us = _graph_us(lambda j: k.gemv_w4a8_f16in(y, x16, Ws[j % ncopy][0], Ws[j % ncopy][1], K, N, 1), 60)
+    nbytes = shapes.gemv_bytes(N, K, 1, 2, "f16")
+    # parity on host-generated operands
+    W, sc16, _ = synth.int4_weights(N, K, 9001)
+    xh = synth.activations_f16(1, K, 9002)
+    xq, xs = oracle.quantize_int8(xh.astype(np.float32))
+    Wd = torch.from_numpy(W).to(dev)
+    scd = torch.from_numpy(sc16.view(np.int16)).to(dev).view(torch.float16)
+    k.gemv_w4a8_f16in(y, torch.from_numpy(xh.view(np.int16)).to(dev).view(torch.float16), Wd, scd, K, N, 1)
+    ref = oracle.gemv_w4a8_f64(xq, xs, W, sc16)
+    got = y.cpu().numpy().astype(np.float64)
+    mar = float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+    dots = torch.empty((N, K // 16), dtype=torch.int32, device=dev)
+    k.gemv_block_dots(dots, torch.from_numpy(xq).to(dev), True, Wd, K, N)
+    dots_equal = bool(np.array_equal(dots.cpu().numpy(), oracle.block_dots_w4a8(W, xq[0])))
+    t0 = time.perf_counter(); oracle.gemv_w4a8_f32(xq, xs, W, sc16, 1); t1 = time.perf_counter()
+    _, cores = oracle.gemv_w4a8_f32(xq, xs, W, sc16, 0)
+    t2 = time.perf_counter(); oracle.gemv_w4a8_f32(xq, xs, W, sc16, 0); t3 = time.perf_counter()
+    return {"workload": "single INT4 GEMV, M=1, K=4096, N=4096 (configs[0])", "us": round(us, 2),
+            "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / peak, 3), "peak_kind": kind,
+            "nominal_frac": round(nbytes / us / 1e3 / 8000.0, 3), "algorithmic_bytes": nbytes,
+            "parity": {"max_abs_rel_vs_f64_oracle": mar, "block_dots_bit_exact": dots_equal},
+            "cpu_port": {"single_thread_us": round((t1 - t0) * 1e6, 1), "all_core_us": round((t3 - t2) * 1e6, 1),
+                         "cores": cores}}
+
+
+def tp_parity(dev, world, rank):
+    """One decode step of a small Qwen3-shaped model at TP-`world` against the same step on one GPU (rank 0 holds the
+    full model beside its shard): every rank slices its shard out of the full matrices of one seed.  Batch 3 runs the
+    dp4a streaming kernel, batch 16 the batched kernel.  Both exchanges are checked."""
+    import torch
+    import torch.distributed as dist
+
+    from blackwell_b200.decode import DecodeEngine
+
+    shape = shapes.ModelShape("tp-parity", layers=2, hidden=1024, inter=2048, n_q_heads=8, n_kv_heads=8, head_dim=128,
+                              vocab=4099)
+    out = {}
+    for exchange in ("peer", "nccl"):
+        for batch in (3, 16):
+            ctx, max_seq = 70, 96
+            eng = DecodeEngine(shape, batch, max_seq, dev, seed=41, world=world, rank=rank, exchange=exchange,
+                               consistent=True)
+            eng.fill_cache_consistent(ctx)
+            toks = [(37 * i + 5) % shape.vocab for i in range(batch)]
+            eng.set_tokens(toks)
+            eng.step()
+            torch.cuda.synchronize()
+            # gather: logits slices (padded to the largest slice), hidden state and ids of every rank
+            vmax = -(-shape.vocab // world)
+            pad = torch.zeros((batch, vmax), dtype=torch.float32, device=dev)
+            pad[:, :eng.v_local].copy_(eng.logits)
+            allp = torch.empty((world, batch, vmax), dtype=torch.float32, device=dev)
+            dist.all_gather_into_tensor(allp.view(-1), pad.view(-1))
+            allx = torch.empty((world,) + tuple(eng.x.shape), dtype=torch.float32, device=dev)
+            dist.all_gather_into_tensor(allx.view(-1), eng.x.contiguous().view(-1))
+            allt = torch.empty((world, batch), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(allt.view(-1), eng.tokens.view(-1))
+            status = 0 if eng.peer is None else eng.peer.status()
+            rec = None
+            if rank == 0:
+                v_base, v_rem = divmod(shape.vocab, world)
+                parts = [allp[r, :, :v_base + (1 if r < v_rem else 0)] for r in range(world)]
+                logits_tp = torch.cat(parts, dim=1)
+                one = DecodeEngine(shape, batch, max_seq, dev, seed=41, world=1, rank=0, consistent=True)
+                one.fill_cache_consistent(ctx)
+                one.set_tokens(toks)
+                one.step()
+                torch.cuda.synchronize()
+                a, b = logits_tp.double(), one.logits.double()
+                rel = float((a - b).abs().max() / b.abs().max())
+                # ids may only differ where the single-GPU top-2 margin is inside the numerical noise
+                top2 = one.logits.topk(2, dim=1).values
+                clear = (top2[:, 0] - top2[:, 1]) > 1e-3 * one.logits.abs().max()
+                ids_equal = bool(torch.equal(allt[0][clear], one.tokens[clear]))
+                rec = {"logits_max_abs_rel": rel, "ids_equal": ids_equal,
+                       "ranks_bit_identical": bool(all(torch.equal(allx[0], allx[r]) and torch.equal(allt[0], allt[r])
+                                                       for r in range(1, world))),
+                       "status": status}
+                del one
+            out["%s_b%d" % (exchange, batch)] = rec
+            del eng
+            torch.cuda.empty_cache()
+            dist.barrier()
+    if rank != 0:
+        return None
+    out["ok"] = bool(all(v["logits_max_abs_rel"] < 1e-3 and v["ids_equal"] and v["ranks_bit_identical"] and
+                         v["status"] == 0 for v in out.values()))
     return out
 
 

@@ -121,8 +121,15 @@ __device__ __forceinline__ unsigned long long bmax64(unsigned long long v, unsig
     return sh[0];
 }
 
+__device__ __forceinline__ float fkey_inverse(unsigned int k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+
+// out_ids (may be null) receives the winning index; cand_out (may be null) the pair {value bits, index + index_offset}
+// that a tensor-parallel caller exchanges instead of its slice of the logits.
 __global__ void __launch_bounds__(256) argmax_batched_kernel(const float* logits, long stride, int vocab,
-                                                             int* out_ids, int* seq_pos_to_advance, int pos_limit) {
+                                                             int* out_ids, int* seq_pos_to_advance, int pos_limit,
+                                                             int2* cand_out, int index_offset) {
     __shared__ unsigned long long sh[32];
     __shared__ bool last;
     const int m = blockIdx.y;
@@ -151,11 +158,30 @@ __global__ void __launch_bounds__(256) argmax_batched_kernel(const float* logits
     }
     b2 = bmax64(b2, sh);
     if (threadIdx.x == 0) {
-        out_ids[m] = (int)(0xFFFFFFFFu - (unsigned int)(b2 & 0xFFFFFFFFull));
+        const int best_idx = (int)(0xFFFFFFFFu - (unsigned int)(b2 & 0xFFFFFFFFull));
+        if (out_ids) out_ids[m] = best_idx;
+        if (cand_out)
+            cand_out[m] = make_int2(__float_as_int(fkey_inverse((unsigned int)(b2 >> 32))), best_idx + index_offset);
         g_bargmax_ticket[m] = 0;
         // positions stop at pos_limit (the last row of the cache), so a replayed step can never index past it
         if (seq_pos_to_advance && (pos_limit <= 0 || seq_pos_to_advance[m] < pos_limit)) seq_pos_to_advance[m] += 1;
     }
+}
+
+// Picks, for every sequence, the best of `world` candidates {value bits, global index} (largest value, lowest index on
+// ties: the rule of the single-GPU argmax), writes the token id and advances the positions as the batched argmax does.
+__global__ void __launch_bounds__(256) argmax_merge_kernel(const int2* cand_all, int world, int M, int* out_ids,
+                                                           int* seq_pos_to_advance, int pos_limit) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    unsigned long long best = 0ull;
+    for (int r = 0; r < world; ++r) {
+        const int2 c = cand_all[(size_t)r * M + m];
+        const unsigned long long key = cand(__int_as_float(c.x), c.y);
+        best = key > best ? key : best;
+    }
+    out_ids[m] = (int)(0xFFFFFFFFu - (unsigned int)(best & 0xFFFFFFFFull));
+    if (seq_pos_to_advance && (pos_limit <= 0 || seq_pos_to_advance[m] < pos_limit)) seq_pos_to_advance[m] += 1;
 }
 
 }  // namespace bw
@@ -197,7 +223,29 @@ extern "C" int bw_sample_argmax_batched(const float* logits, long row_stride, in
     if (blocks > kBatchArgmaxBlocks) blocks = kBatchArgmaxBlocks;
     const dim3 grid(blocks, M);
     argmax_batched_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, row_stride, vocab, out_ids,
-                                                                              seq_pos_to_advance_or_null, pos_limit);
+                                                                              seq_pos_to_advance_or_null, pos_limit,
+                                                                              nullptr, 0);
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+extern "C" int bw_sample_argmax_candidates(const float* logits, long row_stride, int vocab, int M, int index_offset,
+                                           int* cand_out_pairs, void* stream) {
+    if (!logits || !cand_out_pairs || vocab < 1 || M < 1 || M > kBatchArgmaxRows || row_stride < vocab)
+        return cudaErrorInvalidValue;
+    int blocks = (vocab + 256 * 8 - 1) / (256 * 8);
+    if (blocks > kBatchArgmaxBlocks) blocks = kBatchArgmaxBlocks;
+    argmax_batched_kernel<<<dim3(blocks, M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, row_stride, vocab, nullptr, nullptr, 0, reinterpret_cast<int2*>(cand_out_pairs), index_offset);
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+extern "C" int bw_sample_argmax_merge(const int* cand_all_pairs, int world, int M, int* out_ids,
+                                      int* seq_pos_to_advance_or_null, int pos_limit, void* stream) {
+    if (!cand_all_pairs || !out_ids || world < 1 || M < 1) return cudaErrorInvalidValue;
+    argmax_merge_kernel<<<(M + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const int2*>(cand_all_pairs), world, M, out_ids, seq_pos_to_advance_or_null, pos_limit);
     count_launch(1);
     return cudaPeekAtLastError();
 }

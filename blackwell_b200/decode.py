@@ -30,7 +30,10 @@ ROPE_BASE = 1000000.0
 
 class DecodeEngine:
     def __init__(self, shape: ModelShape, batch: int, max_seq: int, device, seed: int = 0, world: int = 1,
-                 rank: int = 0, host_weights=None, exchange: str = "nccl"):
+                 rank: int = 0, host_weights=None, exchange: str = "nccl", consistent: bool = False):
+        """``consistent``: every rank derives its shard from the FULL matrices of one seed (generated on the host, so
+        only for small shapes), which makes a tensor-parallel step comparable with the single-GPU one; otherwise each
+        rank draws its own shard directly in HBM (benchmark sizes)."""
         assert shape.head_dim == 128
         assert shape.n_q_heads % world == 0 and shape.n_kv_heads % world == 0, "heads must split evenly"
         self.s, self.M, self.max_seq, self.dev = shape, batch, max_seq, device
@@ -54,22 +57,24 @@ class DecodeEngine:
         f32, dev = torch.float32, device
         M = batch
 
-        def W(N, K, sd):
+        def W(N, K, sd, kind=None):
             if host_weights is not None:
                 return host_weights(N, K, sd)
+            if consistent:
+                return self._shard_of_full(kind, sd - 17 * rank)
             return synth.int4_weights_device(N, K, sd, device=dev)
 
         self.layers = []
         for l in range(shape.layers):
             sd = seed + 1000 * l + 17 * rank
             L = {
-                "qkv": W(self.qkv_n, H, sd + 1), "o": W(H, self.nq * 128, sd + 2),
-                "gu": W(2 * self.i_local, H, sd + 3), "down": W(H, self.i_local, sd + 4),
+                "qkv": W(self.qkv_n, H, sd + 1, "qkv"), "o": W(H, self.nq * 128, sd + 2, "o"),
+                "gu": W(2 * self.i_local, H, sd + 3, "gu"), "down": W(H, self.i_local, sd + 4, "down"),
                 "rn_in": self._normw(H, seed + 1000 * l + 5), "rn_post": self._normw(H, seed + 1000 * l + 6),
                 "qn": self._normw(128, seed + 1000 * l + 7), "kn": self._normw(128, seed + 1000 * l + 8),
             }
             self.layers.append(L)
-        self.lm = W(self.v_local, H, seed + 900001 + 17 * rank)
+        self.lm = W(self.v_local, H, seed + 900001 + 17 * rank, "lm")
         self.rn_final = self._normw(H, seed + 900002)
         self.embed = synth.activations_f16_device(shape.vocab, H, seed + 900003, device=dev) if host_weights is None \
             else host_weights("embed", shape.vocab, H)
@@ -96,11 +101,56 @@ class DecodeEngine:
             self.peer.connect_processes()
             self.peer_slots = [self.peer.slot(0, M, H), self.peer.slot(1, M, H)]
         if world > 1:
-            self.cand = torch.zeros((M, 2), dtype=f32, device=dev)
-            self.cand_all = torch.zeros((world, M, 2), dtype=f32, device=dev)
+            self.cand = torch.zeros((M, 2), dtype=torch.int32, device=dev)
+            self.cand_all = torch.zeros((world, M, 2), dtype=torch.int32, device=dev)
 
     def _normw(self, n, sd):
         return torch.from_numpy(synth.norm_weight(n, sd)).to(self.dev)
+
+    def _shard_of_full(self, kind, sd):
+        """This rank's shard of the full matrix of seed ``sd``: rows by whole heads (qkv), by the same range of gate
+        and up (gu), by vocabulary range (lm); columns on 32-element boundaries (o: this rank's heads; down: its
+        slice of the intermediate size)."""
+        s, r, w = self.s, self.rank, self.world
+        H, I = s.hidden, s.inter
+        nqf, nkvf = s.n_q_heads, s.n_kv_heads
+        if kind == "qkv":
+            Wf, scf, _ = synth.int4_weights((nqf + 2 * nkvf) * 128, H, sd)
+            rows = np.concatenate([np.arange(r * self.nq * 128, (r + 1) * self.nq * 128),
+                                   nqf * 128 + np.arange(r * self.nkv * 128, (r + 1) * self.nkv * 128),
+                                   (nqf + nkvf) * 128 + np.arange(r * self.nkv * 128, (r + 1) * self.nkv * 128)])
+            Wl, scl = Wf[rows], scf[rows]
+        elif kind == "gu":
+            Wf, scf, _ = synth.int4_weights(2 * I, H, sd)
+            rows = np.concatenate([np.arange(self.i0, self.i0 + self.i_local), I + np.arange(self.i0, self.i0 + self.i_local)])
+            Wl, scl = Wf[rows], scf[rows]
+        elif kind == "lm":
+            Wf, scf, _ = synth.int4_weights(s.vocab, H, sd)
+            Wl, scl = Wf[self.v0:self.v0 + self.v_local], scf[self.v0:self.v0 + self.v_local]
+        elif kind == "o":
+            Wf, scf, _ = synth.int4_weights(H, nqf * 128, sd)
+            k0, kl = r * self.nq * 128, self.nq * 128
+            Wl, scl = Wf[:, k0 // 2:(k0 + kl) // 2], scf[:, k0 // 16:(k0 + kl) // 16]
+        elif kind == "down":
+            Wf, scf, _ = synth.int4_weights(H, I, sd)
+            Wl, scl = Wf[:, self.i0 // 2:(self.i0 + self.i_local) // 2], scf[:, self.i0 // 16:(self.i0 + self.i_local) // 16]
+        else:
+            raise ValueError(kind)
+        Wd = torch.from_numpy(np.ascontiguousarray(Wl)).to(self.dev)
+        sd_ = torch.from_numpy(np.ascontiguousarray(scl).view(np.int16)).to(self.dev).view(torch.float16)
+        return Wd, sd_
+
+    def fill_cache_consistent(self, ctx: int, seed: int = 77):
+        """Like fill_cache, but the cache of the FULL model is drawn on the host from one seed and this rank keeps its
+        kv heads, so that every world size sees the same context (small shapes only)."""
+        full = synth.kv_cache_f16((2, self.M, self.s.layers, self.s.n_kv_heads, ctx, 128), seed)
+        h0 = self.rank * self.nkv
+        for c, src in ((self.kc, full[0]), (self.vc, full[1])):
+            v = c.view(self.M, self.s.layers, self.nkv, self.max_seq, 128)
+            part = np.ascontiguousarray(src[:, :, h0:h0 + self.nkv]).view(np.int16)
+            v[:, :, :, :ctx].copy_(torch.from_numpy(part).to(self.dev).view(torch.float16))
+        self.pos.fill_(ctx - 1)
+        self.ctx_hint = min(self.max_seq, ctx + 64)
 
     # ------------------------------------------------------------------
     def fill_cache(self, ctx: int, seed: int = 77):
@@ -182,19 +232,14 @@ class DecodeEngine:
             self._tp_argmax()
 
     def _tp_argmax(self):
-        """Local argmax, then an all-gather of (value, global index) pairs instead of 600 KB of logits."""
+        """Local argmax into one (value, global index) pair per sequence, an all-gather of the pairs instead of
+        600 KB of logits, and one kernel that picks the winner and advances the positions."""
         import torch.distributed as dist
 
         M = self.M
-        loc = torch.empty((M,), dtype=torch.int32, device=self.dev) if not hasattr(self, "_loc") else self._loc
-        self._loc = loc
-        k.sample_argmax_batched(self.logits, self.v_local, self.v_local, M, loc, self.pos, self.max_seq - 1)
-        idx = loc.long()
-        self.cand[:, 0] = self.logits.gather(1, idx[:, None])[:, 0]
-        self.cand[:, 1] = (idx + self.v0).float()
+        k.sample_argmax_candidates(self.logits, self.v_local, self.v_local, M, self.v0, self.cand)
         dist.all_gather_into_tensor(self.cand_all.view(-1), self.cand.view(-1))
-        best = self.cand_all[:, :, 0].argmax(dim=0)
-        self.tokens.copy_(self.cand_all[best, torch.arange(M, device=self.dev), 1].int())
+        k.sample_argmax_merge(self.cand_all, self.world, M, self.tokens, self.pos, self.max_seq - 1)
 
     # bytes one step must read from HBM on this rank: weights once + the cache rows in use
     def step_bytes(self, ctx: int) -> int:

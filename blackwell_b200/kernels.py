@@ -238,3 +238,13 @@ def sample_argmax_batched(logits, row_stride, vocab, M, out_ids, seq_pos_to_adva
     _chk("sample_argmax_batched", _L.bw_sample_argmax_batched(_p(logits), C.c_long(row_stride), vocab, M,
                                                               _p(out_ids), _p(seq_pos_to_advance), int(pos_limit),
                                                               _s(stream)))
+
+
+def sample_argmax_candidates(logits, row_stride, vocab, M, index_offset, cand_out_pairs, stream=None):
+    _chk("sample_argmax_candidates", _L.bw_sample_argmax_candidates(_p(logits), C.c_long(row_stride), vocab, M,
+                                                                    int(index_offset), _p(cand_out_pairs), _s(stream)))
+
+
+def sample_argmax_merge(cand_all_pairs, world, M, out_ids, seq_pos_to_advance=None, pos_limit=0, stream=None):
+    _chk("sample_argmax_merge", _L.bw_sample_argmax_merge(_p(cand_all_pairs), world, M, _p(out_ids),
+                                                          _p(seq_pos_to_advance), int(pos_limit), _s(stream)))

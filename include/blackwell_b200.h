@@ -174,6 +174,15 @@ int bw_embed_gather_f16(float* x_out, const uint16_t* table_f16, const int* d_to
  * KV cache.  M <= 256. */
 int bw_sample_argmax_batched(const float* logits, long row_stride, int vocab, int M, int* out_ids,
                              int* seq_pos_to_advance_or_null, int pos_limit, void* stream);
+/* Tensor-parallel form of the greedy argmax (the reference is single-GPU: no counterpart): every rank reduces its
+ * own vocabulary slice to one candidate per sequence, cand_out_pairs int32 [M][2] = {bits of the best value,
+ * index + index_offset}; the ranks exchange these 8-byte pairs (an all-gather into [world][M][2]) instead of the
+ * logits, and bw_sample_argmax_merge picks the winner per sequence -- largest value, lowest index on ties, the
+ * single-GPU rule -- into out_ids and advances the positions like bw_sample_argmax_batched. */
+int bw_sample_argmax_candidates(const float* logits, long row_stride, int vocab, int M, int index_offset,
+                                int* cand_out_pairs, void* stream);
+int bw_sample_argmax_merge(const int* cand_all_pairs, int world, int M, int* out_ids,
+                           int* seq_pos_to_advance_or_null, int pos_limit, void* stream);
 
 /* Attention for callers that must not allocate.  No counterpart in the reference: it exists for hosts
  * that cannot reach the CUDA allocator once they are serving -- a process that has given all device memory

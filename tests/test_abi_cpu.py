@@ -12,7 +12,7 @@ import pytest
 from blackwell_b200 import _build, _lib
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REFERENCE = "/root/reference"
+REFERENCE = os.environ.get("BW_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
 
 # Itanium-mangled names the reference's consumers reference (namespace blackwell::kernels).
 DROPIN_SYMBOLS = [

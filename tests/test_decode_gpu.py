@@ -162,6 +162,32 @@ def test_qk_norm_rope_kv_and_embed_and_batched_argmax(cuda):
     assert np.array_equal(p.cpu().numpy(), pos + 2)
 
 
+def test_tensor_parallel_argmax_candidates_and_merge(cuda):
+    """The vocabulary cut into three ranks' slices: per-slice candidates + merge give the ids of the full argmax
+    (ties to the lowest global index) and advance the positions once."""
+    import torch
+
+    from blackwell_b200 import kernels as k
+
+    M, V, world = 5, 10007, 3
+    logits = synth.rng(430).normal(size=(M, V)).astype(np.float32)
+    logits[1, 9000] = logits[1, 17] = logits[1].max() + 1.0      # a tie across two slices -> index 17
+    logits[2, :] = -np.inf                                       # nothing qualifies -> index 0
+    bounds = [0, 3336, 6672, V]
+    cand_all = torch.zeros((world, M, 2), dtype=torch.int32, device="cuda")
+    for r in range(world):
+        sl = to_dev(np.ascontiguousarray(logits[:, bounds[r]:bounds[r + 1]]))
+        n = bounds[r + 1] - bounds[r]
+        k.sample_argmax_candidates(sl, n, n, M, bounds[r], cand_all[r])
+    ids = torch.zeros(M, dtype=torch.int32, device="cuda")
+    pos = to_dev(np.array([0, 1, 2, 3, 9], np.int32))
+    k.sample_argmax_merge(cand_all, world, M, ids, pos, 9)
+    assert [int(i) for i in ids.cpu()] == [oracle.argmax(logits[m]) for m in range(M)]
+    assert pos.cpu().tolist() == [1, 2, 3, 4, 9]
+    vals = cand_all.cpu().numpy()[..., 0].view(np.float32)
+    assert vals[0, 1] == logits[1, 17] and vals[2, 1] == logits[1, 9000]
+
+
 def test_positions_outside_the_cache_are_never_written(cuda):
     """A sequence whose position has reached max_seq (a replayed step that ran past the cache) must leave the cache
     and everything behind it alone, and the batched argmax must stop advancing positions at its limit."""
