@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "../../include/blackwell_b200.h"
+#include "gemv_w4_mma.cuh"
 #include "gemv_w4_stream.cuh"
 #include "host_util.h"
 
@@ -124,6 +125,8 @@ __global__ void __launch_bounds__(128) block_dots_kernel(int32_t* dots, const ui
 // Host side
 // --------------------------------------------------------------------------
 static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0}, g_tune_rg{0}, g_tune_threads{0}, g_tune_tc_min{0};
+static std::atomic<int> g_tune_shrink_ring{1};
+static std::atomic<int> g_tune_mma_slab{0}, g_tune_mma_min{0}, g_tune_mma_max{0}, g_tune_mma_stages{0};
 static std::atomic<long long> g_launches{0};
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -179,8 +182,10 @@ static cudaError_t launch_stream_inst(const GemvArgs& a, const StreamPlan& p, cu
             if (cache_n[dev] < 8) ++cache_n[dev];
         }
     }
-    const int cap = g_tune_ctas.load();
-    if (cap > 0 && occ > cap) occ = cap;
+    // two resident CTAs per SM measured best (they hide each other's barrier and reduction phases); a smaller
+    // footprint leaves the rest of the SM to the next kernel's early CTAs
+    const int cap = g_tune_ctas.load() > 0 ? g_tune_ctas.load() : 2;
+    if (occ > cap) occ = cap;
     const int units = p.n_rows / p.row_unit;
     int grid = sm_count(dev) * occ;
     if (grid > units) grid = units;
@@ -274,6 +279,16 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
     if (S > want) S = want;
     if (S > 8) S = 8;
     if (S < 2) return p;
+    // A CTA never needs more stages than it has tiles: on the small per-layer matrices (a tile or two per CTA) the
+    // spare stages would only keep the next kernel's CTAs from becoming resident early, and with them the weight
+    // prefetch they do ahead of their grid-dependency wait.
+    if (g_tune_shrink_ring.load() != 0) {
+        const int ctas_per_sm = g_tune_ctas.load() > 0 ? g_tune_ctas.load() : 2;
+        const long long grid = (long long)sm_count(current_device()) * ctas_per_sm;
+        const long long rows_per_cta = ((long long)N + grid - 1) / grid;
+        const int tiles = (int)((rows_per_cta + (long long)rg * p.G - 1) / ((long long)rg * p.G));
+        if (S > tiles) S = tiles < 1 ? 1 : tiles;
+    }
     p.S = S;
     p.smem = fixed + (size_t)S * stage;
     p.row_unit = 1;
@@ -284,6 +299,87 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
     p.n_rows = N - N % p.row_unit;
     p.ok = p.n_rows > 0;
     return p;
+}
+
+// ---- tensor-core streaming kernel (mma.sync), 3..16 sequences per launch ----
+// Decides whether it can take the launch and lays out its shared memory: [barriers, flags | prepared activations
+// (a window of K) | ring of S stages | two reduction buffers].
+static bool plan_mma(const GemvArgs& a, int M, int ws_bytes, mma::MmaPlan& p) {
+    const int K = a.K;
+    if (g_tune_force_plain.load() || M < 1 || M > 16 || K % 32 != 0 || a.N < 1) return false;
+    if (!aligned(a.W, 16) || !aligned(a.Wsc, 4) || !aligned(a.x, 16)) return false;
+    if (a.xsc && !aligned(a.xsc, 8)) return false;
+    if (a.x2 && !aligned(a.x2, 16)) return false;
+    if (a.norm_w && !aligned(a.norm_w, 16)) return false;
+    if ((a.xkind == kXHalf) && a.x_stride % 8 != 0) return false;
+    const int MG = M <= 8 ? 1 : 2;
+    const int nch = K / 32;
+    int slab = g_tune_mma_slab.load() > 0 ? g_tune_mma_slab.load() : 64;
+    if (slab > nch) slab = nch;
+    p.slab_cols = slab;
+    p.pitch_n = (slab * 16 + 127) / 128 * 128 + 16;
+    p.pitch_s = (slab * 2 * ws_bytes + 127) / 128 * 128 + 16;
+    // Scale rows and slab widths that are 16-byte multiples travel as bulk copies; otherwise as 8- or 4-byte cp.async
+    // (K % 32 == 0 makes a binary16 scale row a multiple of 4 bytes and an fp32 one a multiple of 8).
+    const size_t scale_row = (size_t)(K / 16) * ws_bytes;
+    p.scale_gran = 4;
+    for (int gran = 16; gran >= 4; gran /= 2)
+        if (scale_row % gran == 0 && ((size_t)slab * 2 * ws_bytes) % gran == 0 && aligned(a.Wsc, gran)) { p.scale_gran = gran; break; }
+    if (scale_row % 4 != 0 || !aligned(a.Wsc, 4)) return false;
+    const size_t stage = (size_t)mma::kRows * (p.pitch_n + p.pitch_s);
+    const size_t red = (size_t)2 * mma::kConsumerWarps * mma::kRows * mma::red_stride(MG) * sizeof(float);
+    const size_t fixed = mma::Smem::kX;
+    const size_t xcol = (size_t)MG * mma::kXColBytes;
+    const size_t total = (size_t)kMaxDynSmem;
+    const int nslab = (nch + slab - 1) / slab;
+    // Prefer the whole K prepared at once with the deepest ring that fits (at most 4 stages); otherwise two stages
+    // and as wide a window as fits.
+    int S = g_tune_mma_stages.load() > 0 ? g_tune_mma_stages.load() : 4;
+    if (S > 8) S = 8;
+    for (; S >= 2; --S)
+        if (fixed + align128(xcol * nch) + S * stage + red <= total) break;
+    if (S >= 2) {
+        p.win_cols = nch;
+    } else {
+        S = 2;
+        if (fixed + S * stage + red + xcol * slab > total) return false;
+        const size_t avail = total - fixed - S * stage - red;
+        int wc = (int)(avail / xcol) / slab * slab;
+        if (wc < slab) return false;
+        // equal windows rather than a full one and a sliver
+        const int nwin = (nslab * slab + wc - 1) / wc;
+        wc = ((nslab + nwin - 1) / nwin) * slab;
+        p.win_cols = wc;
+    }
+    p.S = S;
+    p.x_off = fixed;
+    p.stage_off = fixed + align128(xcol * (size_t)(p.win_cols < nch ? p.win_cols : nch));
+    p.red_off = p.stage_off + (size_t)S * stage;
+    p.smem = p.red_off + red;
+    return p.smem <= total;
+}
+
+template <int MG, typename WS>
+static cudaError_t launch_mma_inst(const GemvArgs& a, const mma::MmaPlan& p, int M, cudaStream_t st) {
+    auto kern = mma::gemv_w4_mma_kernel<MG, WS>;
+    static std::once_flag once[kMaxDevices];
+    const int dev = current_device();
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(once[dev], [&] {
+        attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem);
+    });
+    if (attr_err != cudaSuccess) return attr_err;
+    int grid = sm_count(dev);  // one persistent CTA per SM; at least 8 rows each
+    const int by_rows = (a.N + 7) / 8;
+    if (grid > by_rows) grid = by_rows;
+    cudaError_t le = launch_pdl(kern, dim3(grid), dim3(mma::kThreads), p.smem, st, a, p, M);
+    count_launch(1);
+    return le != cudaSuccess ? le : cudaPeekAtLastError();
+}
+
+template <typename WS>
+static cudaError_t launch_mma(const GemvArgs& a, const mma::MmaPlan& p, int M, cudaStream_t st) {
+    return M <= 8 ? launch_mma_inst<1, WS>(a, p, M, st) : launch_mma_inst<2, WS>(a, p, M, st);
 }
 
 template <typename WS>
@@ -299,8 +395,15 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
     if (a.y_stride <= 0) a.y_stride = a.N;
     if (a.x_stride % 4 != 0 || a.y_stride < a.N) return cudaErrorInvalidValue;
     if (!prequant && !aligned(a.x, 16)) return cudaErrorInvalidValue;
-    // Batches above the dp4a kernel's range go to the tensor cores, up to 64 sequences per launch.
-    const int tc_min = g_tune_tc_min.load() > 0 ? g_tune_tc_min.load() : 8;  // measured: at 8 sequences the MMA path already wins
+    // 3..16 sequences: the streaming kernel with warp-level tensor-core dots, either scale type.
+    const int mma_min = g_tune_mma_min.load() > 0 ? g_tune_mma_min.load() : 3;
+    const int mma_max = g_tune_mma_max.load() > 0 ? g_tune_mma_max.load() : 16;
+    if (M >= mma_min && M <= mma_max && M <= 16) {
+        mma::MmaPlan mp;
+        if (plan_mma(a, M, (int)sizeof(WS), mp)) return launch_mma<WS>(a, mp, M, st);
+    }
+    // Larger batches go to the tcgen05 kernel, up to 64 sequences per launch.
+    const int tc_min = g_tune_tc_min.load() > 0 ? g_tune_tc_min.load() : 8;
     if (sizeof(WS) == 2 && M >= tc_min && tc::eligible(a, M < 64 ? M : 64)) {
         for (int m0 = 0; m0 < M; m0 += 64) {
             const int mc = (M - m0) < 64 ? (M - m0) : 64;
@@ -322,15 +425,28 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
         return cudaSuccess;
     }
     if (!prequant && M > 8) return cudaErrorInvalidValue;
-    // M > 8: passes of up to 8 sequences (pre-quantized operands only).
-    for (int m0 = 0; m0 < M; m0 += 8) {
-        const int mc = (M - m0) < 8 ? (M - m0) : 8;
+    // M > 8: passes of up to 16 (tensor-core streaming kernel) or 8 sequences (pre-quantized operands only).
+    int pass = 8;
+    if (M > 8 && mma_max >= 16) {
+        mma::MmaPlan mp;
+        if (plan_mma(a, 16, (int)sizeof(WS), mp)) pass = 16;
+    }
+    for (int m0 = 0; m0 < M; m0 += pass) {
+        const int mc = (M - m0) < pass ? (M - m0) : pass;
         GemvArgs b = a;
         b.y = a.y + (size_t)m0 * a.y_stride;
         if (a.residual) b.residual = a.residual + (size_t)m0 * a.y_stride;
         if (a.xkind == kXInt8) b.x = static_cast<const int8_t*>(a.x) + (size_t)m0 * a.K;
         if (a.xkind == kXInt4) b.x = static_cast<const uint8_t*>(a.x) + (size_t)m0 * (a.K / 2);
         if (a.xsc) b.xsc = a.xsc + (size_t)m0 * (a.K / 16);
+        if (mc >= mma_min && mc <= mma_max) {
+            mma::MmaPlan mp;
+            if (plan_mma(b, mc, (int)sizeof(WS), mp)) {
+                cudaError_t e = launch_mma<WS>(b, mp, mc, st);
+                if (e != cudaSuccess) return e;
+                continue;
+            }
+        }
         const StreamPlan p = plan_stream(b, mc, (int)sizeof(WS));
         int done = 0;
         if (p.ok) {
@@ -477,6 +593,11 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 9: set_attn_mma(value); return 0;
         case 10: peer::set_two_step_min_kb(value); return 0;
         case 11: peer::set_wait_limit_ms(value); return 0;
+        case 12: g_tune_mma_slab = value; return 0;
+        case 13: g_tune_mma_min = value; return 0;
+        case 14: g_tune_mma_max = value; return 0;
+        case 15: g_tune_mma_stages = value; return 0;
+        case 16: g_tune_shrink_ring = value; return 0;
         default: return cudaErrorInvalidValue;
     }
 }

@@ -1,0 +1,344 @@
+// Streaming INT4 block-16 GEMV for 3..16 sequences per launch on sm_100a: the weight stream of the small-batch
+// kernel (bulk copies into a shared-memory ring) with the integer dot products on the warp-level tensor-core
+// instruction mma.sync.m16n8k32.s8 instead of dp4a, so that the instruction count per weight byte no longer
+// grows with the number of sequences.
+//
+//   y[m][n] = sum_kb dot16(W[n,kb], xq[m,kb]) * w_sc[n,kb] * x_sc[m,kb]
+//
+// Work decomposition.  A persistent CTA owns a contiguous range of output rows and walks it in tiles of 32 rows;
+// a tile is streamed in slabs of kSlabCols 32-k columns (1 KB of nibbles per row).  A producer warp (lane = row)
+// issues one bulk copy per row and slab for the nibbles and one for the scales into a ring stage whose row pitch is
+// padded to 16 mod 128 bytes, which makes the ldmatrix reads below conflict-free.  Eight consumer warps split the
+// columns of a slab.  For one column (32 k = two k-blocks) of the 32 rows a warp
+//   * reads the packed nibbles with one ldmatrix.x4: thread (g, t) of the warp gets word t of rows g, g+8, g+16, g+24,
+//   * turns each word into 16*q signed bytes of its even-k and odd-k nibbles (LOP3): exactly the A fragment
+//     {a0, a1, a2, a3} of an m16n8k32 MMA whose k slots are (t, even) and (t, odd),
+//   * multiplies with the B fragment of eight sequences, prepared once per CTA in the same k-slot order.  A k-block
+//     is 16 k but the instruction sums 32: it is issued twice, once with the second block's B lanes zeroed and once
+//     with the first's, so each accumulator tile is the exact int32 dot of ONE block.  Accumulators start from the
+//     bit pattern of 1.5 * 2^23, so the result read as a float is 12582912 + 16 * dot exactly,
+//   * applies the scales with packed fp32 FMAs: t = fma(F, w, -12582912 w) (exact for binary16 w; for fp32 scales
+//     F - 12582912 first), acc = fma(t, x_sc / 16, acc).
+// Each (row, sequence) accumulator lives in exactly one thread of the warp; after the last slab of a tile the eight
+// warps' partial sums are added through shared memory in fixed order (deterministic) and stored.
+//
+// When the prepared activations of all K do not fit beside the ring, K is processed in windows: the CTA prepares a
+// window, runs all its row tiles over the window's slabs and accumulates into y (its rows are its own).
+// Every wait is bounded (common.cuh); a wait that gives up raises the CTA's abort flag and the status word.
+#pragma once
+#include "gemv_w4_stream.cuh"
+
+namespace bw {
+namespace mma {
+
+constexpr int kRows = 32;          // rows per tile
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kXColBytes = 320;    // prepared activations of one (column, group of 8 sequences): B fragments + scales
+__host__ __device__ constexpr int red_stride(int MG) { return 8 * MG + 1; }  // floats per row of a warp's partial sums (odd: no bank conflicts)
+
+struct MmaPlan {
+    int slab_cols;      // 32-k columns per slab
+    int win_cols;       // columns per activation window (multiple of slab_cols, or all)
+    int S;              // ring stages
+    int pitch_n;        // bytes between rows of a stage: nibbles
+    int pitch_s;        //                                 scales
+    int scale_gran;     // 16: one bulk copy per scale row; 8 or 4: cp.async of that size (rows not 16-byte aligned in HBM)
+    size_t x_off, stage_off, red_off, smem;
+};
+
+struct Smem {
+    static constexpr int kFull = 0;        // S mbarriers
+    static constexpr int kEmpty = 64;      // S mbarriers
+    static constexpr int kAbort = 128;
+    static constexpr int kRstd = 192;      // 16 floats
+    static constexpr int kScratch = 256;   // 16 x 8 floats for the norm's block reduction
+    static constexpr int kX = 1024;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+// D = A (16 x 32, s8) * B (32 x 8, s8) + C, int32.
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1, int c) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
+}
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    unsigned long long A, B, C, D;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(A) : "f"(a0), "f"(a1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(B) : "f"(b0), "f"(b1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(C) : "f"(c0), "f"(c1));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(D) : "l"(A), "l"(B), "l"(C));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(D));
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
+
+template <typename WS> struct ScalePairF;
+template <> struct ScalePairF<__half> {
+    static __device__ __forceinline__ float2 load(const unsigned char* p) {
+        return __half22float2(*reinterpret_cast<const __half2*>(p));
+    }
+};
+template <> struct ScalePairF<float> {
+    static __device__ __forceinline__ float2 load(const unsigned char* p) { return *reinterpret_cast<const float2*>(p); }
+};
+
+// MG groups of 8 sequences (M <= 8 MG); WS = weight scale type.
+template <int MG, typename WS>
+__global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs a, const MmaPlan p, int M) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int K = a.K, nch = a.nch, S = p.S;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + Smem::kFull);
+    uint64_t* empty = reinterpret_cast<uint64_t*>(smem + Smem::kEmpty);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kAbort);
+    float* rstd_s = reinterpret_cast<float*>(smem + Smem::kRstd);
+    float* nscratch = reinterpret_cast<float*>(smem + Smem::kScratch);
+    unsigned char* xbase = smem + p.x_off;
+    unsigned char* stages = smem + p.stage_off;
+    float* red = reinterpret_cast<float*>(smem + p.red_off);
+    const size_t stage_bytes = (size_t)kRows * (p.pitch_n + p.pitch_s);
+    const size_t stage_sc = (size_t)kRows * p.pitch_n;  // scales follow the nibbles inside a stage
+
+    // this CTA's rows
+    const int row_begin = (int)(((long long)a.N * blockIdx.x) / gridDim.x);
+    const int row_end = (int)(((long long)a.N * (blockIdx.x + 1)) / gridDim.x);
+    const int ntiles = (row_end - row_begin + kRows - 1) / kRows;
+    const int nwin = (nch + p.win_cols - 1) / p.win_cols;
+
+    if (t == 0) {
+        // full: one arrive.expect_tx by the producer's lane 0, plus (unaligned scale rows) one cp.async arrival per lane
+        for (int s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&full[s]), p.scale_gran == 16 ? 1 : 33);
+            mbar_init(smem_u32(&empty[s]), kConsumerWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_trigger();
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------------ producer: lane = row of the tile
+        const uint64_t policy = l2_policy_evict_first();
+        const int ws = (int)sizeof(WS);
+        int item = 0;
+        bool ok = true;
+        for (int w = 0; w < nwin && ok; ++w) {
+            const int wc0 = w * p.win_cols, wc1 = min(nch, wc0 + p.win_cols);
+            for (int tile = 0; tile < ntiles && ok; ++tile) {
+                const int r0 = row_begin + tile * kRows;
+                const int rows = min(kRows, row_end - r0);
+                for (int c0 = wc0; c0 < wc1; c0 += p.slab_cols, ++item) {
+                    const int cols = min(p.slab_cols, wc1 - c0);
+                    const int s = item % S;
+                    if (item >= S) {
+                        if (!mbar_wait(smem_u32(&empty[s]), ((item / S) & 1) ^ 1)) { *abort_flag = 1; ok = false; break; }
+                    }
+                    if (*abort_flag) { ok = false; break; }
+                    const uint32_t fb = smem_u32(&full[s]);
+                    const uint32_t nb = (uint32_t)cols * 16u, sb = (uint32_t)cols * 2u * ws;
+                    if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows * (nb + (p.scale_gran == 16 ? sb : 0u)));
+                    __syncwarp();
+                    unsigned char* st = stages + (size_t)s * stage_bytes;
+                    if (lane < rows) {
+                        const size_t grow = (size_t)(r0 + lane);
+                        bulk_g2s(smem_u32(st + (size_t)lane * p.pitch_n), a.W + grow * (size_t)(K / 2) + (size_t)c0 * 16, nb,
+                                 fb, policy);
+                        const unsigned char* ssrc = static_cast<const unsigned char*>(a.Wsc) +
+                                                    (grow * (size_t)(K / 16) + (size_t)c0 * 2) * ws;
+                        unsigned char* sdst = st + stage_sc + (size_t)lane * p.pitch_s;
+                        if (p.scale_gran == 16) {
+                            bulk_g2s(smem_u32(sdst), ssrc, sb, fb, policy);
+                        } else if (p.scale_gran == 8) {
+                            for (uint32_t o = 0; o < sb; o += 8) cp_async8(smem_u32(sdst + o), ssrc + o);
+                        } else {
+                            for (uint32_t o = 0; o < sb; o += 4) cp_async4(smem_u32(sdst + o), ssrc + o);
+                        }
+                    }
+                    if (p.scale_gran != 16) cp_async_arrive_noinc(fb);
+                }
+            }
+        }
+        if (p.scale_gran != 16) asm volatile("cp.async.wait_all;" ::: "memory");
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumers
+    const int g = lane >> 2, tq = lane & 3;
+    const int ct = t;  // consumer thread index 0..255
+    pdl_wait();        // the activations (and y, the residual) come from the kernels before
+
+    float acc[2][2][MG][2];  // [row group][row g / g+8][sequence group][sequence 2t / 2t+1]
+    int item = 0;
+    bool ok = true;
+    int tile_count = 0;
+
+    for (int w = 0; w < nwin; ++w) {
+        const int wc0 = w * p.win_cols, wc1 = min(nch, wc0 + p.win_cols);
+        // ---- prepare the window's activations: B fragments in k-slot order and block scales / 16
+        if (w > 0) consumer_sync();  // every warp is done with the previous window's fragments
+        const bool needs_norm = (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4);
+        if (needs_norm && w == 0) {
+            for (int m = 0; m < M; ++m) {
+                float ss = 0.f;
+                const float4* px = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * a.x_stride);
+                for (int i = ct; i < K / 4; i += kConsumerWarps * 32) {
+                    const float4 f = __ldg(px + i);
+                    ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); ss = fmaf(f.z, f.z, ss); ss = fmaf(f.w, f.w, ss);
+                }
+                ss = warp_sum(ss);
+                if (lane == 0) nscratch[m * kConsumerWarps + warp] = ss;
+            }
+            consumer_sync();
+            if (ct < M) {
+                float tot = 0.f;
+                for (int i = 0; i < kConsumerWarps; ++i) tot += nscratch[ct * kConsumerWarps + i];
+                rstd_s[ct] = rsqrtf(tot / (float)K + a.eps);
+            }
+            consumer_sync();
+        }
+        {
+            const int wcols = wc1 - wc0;
+            const int nblk = 2 * wcols * 8 * MG;  // (column, block of the column, sequence)
+            for (int idx = ct; idx < nblk; idx += kConsumerWarps * 32) {
+                const int m = idx % (8 * MG);
+                const int cb = idx / (8 * MG);
+                const int cl = cb >> 1, blk = cb & 1;
+                uint32_t e[2] = {0u, 0u}, o[2] = {0u, 0u};
+                float sc = 0.f;
+                if (m < M) make_xblock(a, m, 2 * (wc0 + cl) + blk, needs_norm ? rstd_s[m] : 1.f, e, o, sc);
+                unsigned char* xc = xbase + ((size_t)cl * MG + (m >> 3)) * kXColBytes;
+                // lanes (g = m % 8, t = 2 blk) and (g, 2 blk + 1): {even-k bytes, odd-k bytes} of the block's two words
+                uint2* bf = reinterpret_cast<uint2*>(xc) + (m & 7) * 4 + 2 * blk;
+                bf[0] = make_uint2(e[0], o[0]);
+                bf[1] = make_uint2(e[1], o[1]);
+                // scales: per pair of sequences (2t, 2t+1): {A 2t, A 2t+1, B 2t, B 2t+1}
+                float* sf = reinterpret_cast<float*>(xc + 256) + ((m & 7) >> 1) * 4 + 2 * blk + (m & 1);
+                *sf = sc;
+            }
+            consumer_sync();
+        }
+
+        for (int tile = 0; tile < ntiles; ++tile, ++tile_count) {
+            const int r0 = row_begin + tile * kRows;
+            const int rows = min(kRows, row_end - r0);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < MG; ++c) { acc[i][h][c][0] = 0.f; acc[i][h][c][1] = 0.f; }
+
+            for (int c0 = wc0; c0 < wc1; c0 += p.slab_cols, ++item) {
+                const int cols = min(p.slab_cols, wc1 - c0);
+                const int s = item % S;
+                if (ok && !mbar_wait(smem_u32(&full[s]), (item / S) & 1)) { *abort_flag = 1; ok = false; }
+                if (ok) {
+                    const unsigned char* st = stages + (size_t)s * stage_bytes;
+                    const uint32_t st_n = smem_u32(st) + (uint32_t)lane * p.pitch_n;
+                    const unsigned char* st_s = st + stage_sc + (size_t)g * p.pitch_s;
+#pragma unroll 2
+                    for (int cl = warp; cl < cols; cl += kConsumerWarps) {
+                        uint32_t r[4];
+                        ldmatrix_x4(st_n + 16u * cl, r);
+                        uint32_t lo[4], hi[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) nibbles_to_s8x16(r[j], lo[j], hi[j]);
+                        float2 wsc[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            wsc[j] = ScalePairF<WS>::load(st_s + (size_t)(8 * j) * p.pitch_s + (size_t)cl * (2 * sizeof(WS)));
+                        const unsigned char* xc = xbase + (size_t)(c0 - wc0 + cl) * MG * kXColBytes;
+#pragma unroll
+                        for (int c = 0; c < MG; ++c) {
+                            const uint2 bf = *reinterpret_cast<const uint2*>(xc + c * kXColBytes + lane * 8);
+                            const float4 xs = *reinterpret_cast<const float4*>(xc + c * kXColBytes + 256 + tq * 16);
+                            // block A lives in the k slots of lanes t = 0, 1, block B in those of t = 2, 3
+                            const uint32_t bA0 = tq < 2 ? bf.x : 0u, bA1 = tq < 2 ? bf.y : 0u;
+                            const uint32_t bB0 = tq < 2 ? 0u : bf.x, bB1 = tq < 2 ? 0u : bf.y;
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                int dA[4], dB[4];
+                                mma_s8(dA, lo[2 * i], lo[2 * i + 1], hi[2 * i], hi[2 * i + 1], bA0, bA1, kMagicInt);
+                                mma_s8(dB, lo[2 * i], lo[2 * i + 1], hi[2 * i], hi[2 * i + 1], bB0, bB1, kMagicInt);
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    const float2 w2 = wsc[2 * i + h];
+                                    float tA0, tA1, tB0, tB1;
+                                    if (sizeof(WS) == 2) {
+                                        const float cA = -kMagicFloat * w2.x, cB = -kMagicFloat * w2.y;  // exact
+                                        ffma2(tA0, tA1, __int_as_float(dA[2 * h]), __int_as_float(dA[2 * h + 1]), w2.x, w2.x, cA, cA);
+                                        ffma2(tB0, tB1, __int_as_float(dB[2 * h]), __int_as_float(dB[2 * h + 1]), w2.y, w2.y, cB, cB);
+                                    } else {
+                                        tA0 = (__int_as_float(dA[2 * h]) - kMagicFloat) * w2.x;
+                                        tA1 = (__int_as_float(dA[2 * h + 1]) - kMagicFloat) * w2.x;
+                                        tB0 = (__int_as_float(dB[2 * h]) - kMagicFloat) * w2.y;
+                                        tB1 = (__int_as_float(dB[2 * h + 1]) - kMagicFloat) * w2.y;
+                                    }
+                                    ffma2(acc[i][h][c][0], acc[i][h][c][1], tA0, tA1, xs.x, xs.y, acc[i][h][c][0], acc[i][h][c][1]);
+                                    ffma2(acc[i][h][c][0], acc[i][h][c][1], tB0, tB1, xs.z, xs.w, acc[i][h][c][0], acc[i][h][c][1]);
+                                }
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&empty[s]));  // this warp is done with the stage
+            }
+
+            // ---- the eight warps' partial sums of the tile -> y
+            constexpr int RS = red_stride(MG);
+            float* rb = red + (size_t)(tile_count & 1) * (kConsumerWarps * kRows * RS);
+            float* mine = rb + (size_t)warp * (kRows * RS);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int c = 0; c < MG; ++c) {
+                        float* dst = mine + (16 * i + 8 * h + g) * RS + 8 * c + 2 * tq;
+                        dst[0] = acc[i][h][c][0];
+                        dst[1] = acc[i][h][c][1];
+                    }
+            consumer_sync();
+            if (*abort_flag) ok = false;
+            if (ok) {
+                for (int o = ct; o < kRows * 8 * MG; o += kConsumerWarps * 32) {
+                    const int row = o & (kRows - 1), m = o >> 5;
+                    if (row < rows && m < M) {
+                        float sum = 0.f;
+#pragma unroll
+                        for (int wv = 0; wv < kConsumerWarps; ++wv) sum += rb[(size_t)wv * (kRows * RS) + row * RS + m];
+                        const size_t yi = (size_t)m * a.y_stride + r0 + row;
+                        if (w == 0) a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
+                        else a.y[yi] += sum;
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && ct == 0) {
+        // give copies still in flight a bounded chance to land before the CTA's shared memory is released
+        for (int s = 0; s < S; ++s) (void)mbar_wait(smem_u32(&full[s]), 0);
+        atomicExch(a.status, kStatusMbarTimeout);
+    }
+}
+
+}  // namespace mma
+}  // namespace bw

@@ -286,7 +286,10 @@ int bw_reserve_scratch(size_t gemv_bytes, size_t attention_bytes);
  * key 8 = programmatic dependent launch on (1, default) / off (0), key 9 = tensor-core attention kernel
  * for the binary16 cache on (1, default) / off (0: scalar kernel, for comparison runs), key 10 = smallest vector in
  * KiB that the peer all-reduce sums in two steps on four or more ranks (0 = default 4096), key 11 = longest wait of
- * the peer all-reduce for another rank in milliseconds (0 = default, about 2000). */
+ * the peer all-reduce for another rank in milliseconds (0 = default, about 2000), key 12 = 32-k columns per slab of
+ * the mma.sync streaming kernel (0 = default 64), keys 13 / 14 = smallest / largest batch it takes (0 = defaults 3 and
+ * 16; a smallest batch above 16 switches it off), key 15 = its ring stages (0 = automatic), key 16 = shrink the
+ * small-batch kernel's ring to the tiles a CTA has (1, default) or not (0). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);
