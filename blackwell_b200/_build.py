@@ -3,7 +3,8 @@
 ``python -m blackwell_b200._build`` compiles every ``csrc/*.cu`` with nvcc
 (``-gencode arch=compute_100a,code=sm_100a -lineinfo``), one object per source in
 parallel, and links them into ``blackwell_b200/lib/libblackwell_kernels.so`` and
-the static ``libblackwell_kernels.a`` the reference's consumers link against.
+the static ``libblackwell_kernels.a`` the reference's consumers link against, and builds the JSON-lines daemon
+``blackwell_b200/lib/inference_server_w4a8`` from ``daemon/``.
 No GPU is needed to build.
 """
 from __future__ import annotations
@@ -20,6 +21,8 @@ LIBDIR = os.path.join(HERE, "lib")
 OBJDIR = os.path.join(LIBDIR, "obj")
 SO = os.path.join(LIBDIR, "libblackwell_kernels.so")
 AR = os.path.join(LIBDIR, "libblackwell_kernels.a")
+DAEMON_SRC = os.path.join(HERE, "daemon", "inference_server_w4a8.cpp")
+DAEMON = os.path.join(LIBDIR, "inference_server_w4a8")
 
 # IEEE division and square root are requested explicitly: the quantizers must
 # round exactly like the reference's (v / sc, roundf).
@@ -75,6 +78,13 @@ def build(verbose: bool = False, force: bool = False, extra: list[str] | None = 
         if os.path.exists(AR):
             os.remove(AR)
         subprocess.check_call(["ar", "rcs", AR, *objs])
+    # the JSON-lines daemon on the decode-step driver: host C++ above the C ABI, linked against the shared library
+    if not os.path.exists(DAEMON) or os.path.getmtime(DAEMON) < max(os.path.getmtime(DAEMON_SRC), os.path.getmtime(SO)):
+        cmd = ["nvcc", "-std=c++17", "-O2", "-Wno-deprecated-gpu-targets", "-o", DAEMON, DAEMON_SRC, "-L" + LIBDIR, "-lblackwell_kernels", "-cudart",
+               "shared", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
     return SO
 
 

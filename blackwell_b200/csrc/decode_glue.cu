@@ -83,6 +83,39 @@ __global__ void __launch_bounds__(256) embed_gather_kernel(float* x, const __hal
     o[1] = b;
 }
 
+// x[m][:] = table[token[m]][:] for an fp32 table (the reference dequantizes its INT4 embedding to fp32 once at start-up:
+// server/inference_server_int4_batched.cu:196-217).
+__global__ void __launch_bounds__(256) embed_gather_f32_kernel(float* x, const float* table, const int* tokens, int H,
+                                                               int vocab) {
+    const int m = blockIdx.y;
+    int tok = tokens[m];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= H) return;
+    *reinterpret_cast<float4*>(x + (size_t)m * H + i) = __ldg(reinterpret_cast<const float4*>(table + (size_t)tok * H + i));
+}
+
+// Token bookkeeping of a batched generation that never leaves the GPU.  Sequence m has a prompt of prompt_len[m] ids
+// in prompt[m][0 .. max_prompt) and stands at position pos[m] (the index of the token it consumes in this step).
+//   select: the step's input id = the prompt's id at that position while the prompt lasts, else the id sampled by
+//           the previous step;
+//   record: after sampling (pos already advanced to the new token's index p), a token beyond the prompt is the
+//           sequence's generated token number p - prompt_len[m], stored in gen[m][..] if it is one of the first max_new.
+__global__ void select_input_tokens_kernel(int* tokens_in, const int* sampled, const int* prompt, const int* prompt_len,
+                                           const int* pos, int M, int max_prompt) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    const int p = pos[m];
+    tokens_in[m] = (p >= 0 && p < prompt_len[m] && p < max_prompt) ? prompt[(size_t)m * max_prompt + p] : sampled[m];
+}
+__global__ void record_generated_kernel(int* gen, const int* sampled, const int* prompt_len, const int* pos, int M,
+                                        int max_new) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    const int j = pos[m] - prompt_len[m];
+    if (j >= 0 && j < max_new) gen[(size_t)m * max_new + j] = sampled[m];
+}
+
 // Greedy argmax of every row of logits [M][stride], with the candidate rule of the single-row kernel (start at
 // (-1e38, 0), strict '>', lowest index on ties).  Optionally advances the per-sequence positions by one, which
 // closes the decode step inside a CUDA graph.
@@ -211,6 +244,34 @@ extern "C" int bw_embed_gather_f16(float* x_out, const uint16_t* table_f16, cons
     const dim3 grid((H / 8 + 255) / 256, M);
     embed_gather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         x_out, reinterpret_cast<const __half*>(table_f16), d_tokens, H, vocab);
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+extern "C" int bw_embed_gather_f32(float* x_out, const float* table_f32, const int* d_tokens, int H, int vocab, int M,
+                                   void* stream) {
+    if (!x_out || !table_f32 || !d_tokens || H < 4 || H % 4 != 0 || vocab < 1 || M < 1) return cudaErrorInvalidValue;
+    const dim3 grid((H / 4 + 255) / 256, M);
+    embed_gather_f32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x_out, table_f32, d_tokens, H, vocab);
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+extern "C" int bw_select_input_tokens(int* tokens_in, const int* sampled, const int* prompt, const int* prompt_len,
+                                      const int* d_seq_pos, int M, int max_prompt, void* stream) {
+    if (!tokens_in || !sampled || !prompt || !prompt_len || !d_seq_pos || M < 1 || max_prompt < 1)
+        return cudaErrorInvalidValue;
+    select_input_tokens_kernel<<<(M + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        tokens_in, sampled, prompt, prompt_len, d_seq_pos, M, max_prompt);
+    count_launch(1);
+    return cudaPeekAtLastError();
+}
+
+extern "C" int bw_record_generated(int* gen, const int* sampled, const int* prompt_len, const int* d_seq_pos, int M,
+                                   int max_new, void* stream) {
+    if (!gen || !sampled || !prompt_len || !d_seq_pos || M < 1 || max_new < 1) return cudaErrorInvalidValue;
+    record_generated_kernel<<<(M + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(gen, sampled, prompt_len,
+                                                                                           d_seq_pos, M, max_new);
     count_launch(1);
     return cudaPeekAtLastError();
 }

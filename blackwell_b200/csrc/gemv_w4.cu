@@ -4,6 +4,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <string.h>
+
 #include <atomic>
 #include <mutex>
 
@@ -126,6 +128,11 @@ __global__ void __launch_bounds__(128) block_dots_kernel(int32_t* dots, const ui
 // --------------------------------------------------------------------------
 static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0}, g_tune_rg{0}, g_tune_threads{0}, g_tune_tc_min{0};
 static std::atomic<int> g_tune_shrink_ring{1};
+static std::atomic<int> g_tune_mma_mode{0};
+#ifdef BW_GEMV_TIMELINE
+static unsigned long long* g_timeline_ptr = nullptr;
+extern "C" void bw_debug_set_timeline(void* dev_ptr) { g_timeline_ptr = static_cast<unsigned long long*>(dev_ptr); }
+#endif
 static std::atomic<int> g_tune_mma_slab{0}, g_tune_mma_min{0}, g_tune_mma_max{0}, g_tune_mma_stages{0};
 static std::atomic<long long> g_launches{0};
 
@@ -304,30 +311,30 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
 // ---- tensor-core streaming kernel (mma.sync), 3..16 sequences per launch ----
 // Decides whether it can take the launch and lays out its shared memory: [barriers, flags | prepared activations
 // (a window of K) | ring of S stages | two reduction buffers].
-static bool plan_mma(const GemvArgs& a, int M, int ws_bytes, mma::MmaPlan& p) {
+static bool plan_mma_slab(const GemvArgs& a, int M, int ws_bytes, int slab, mma::MmaPlan& p, bool* whole_k) {
     const int K = a.K;
-    if (g_tune_force_plain.load() || M < 1 || M > 16 || K % 32 != 0 || a.N < 1) return false;
-    if (!aligned(a.W, 16) || !aligned(a.Wsc, 4) || !aligned(a.x, 16)) return false;
-    if (a.xsc && !aligned(a.xsc, 8)) return false;
-    if (a.x2 && !aligned(a.x2, 16)) return false;
-    if (a.norm_w && !aligned(a.norm_w, 16)) return false;
-    if ((a.xkind == kXHalf) && a.x_stride % 8 != 0) return false;
     const int MG = M <= 8 ? 1 : 2;
     const int nch = K / 32;
-    int slab = g_tune_mma_slab.load() > 0 ? g_tune_mma_slab.load() : 64;
     if (slab > nch) slab = nch;
     p.slab_cols = slab;
     p.pitch_n = (slab * 16 + 127) / 128 * 128 + 16;
+    p.ablate = g_tune_mma_mode.load();
     p.pitch_s = (slab * 2 * ws_bytes + 127) / 128 * 128 + 16;
-    // Scale rows and slab widths that are 16-byte multiples travel as bulk copies; otherwise as 8- or 4-byte cp.async
-    // (K % 32 == 0 makes a binary16 scale row a multiple of 4 bytes and an fp32 one a multiple of 8).
+    // Scales travel as cp.async of the largest size the rows' alignment in HBM allows (K % 32 == 0 makes a binary16
+    // scale row a multiple of 4 bytes and an fp32 one a multiple of 8).
     const size_t scale_row = (size_t)(K / 16) * ws_bytes;
     p.scale_gran = 4;
     for (int gran = 16; gran >= 4; gran /= 2)
         if (scale_row % gran == 0 && ((size_t)slab * 2 * ws_bytes) % gran == 0 && aligned(a.Wsc, gran)) { p.scale_gran = gran; break; }
     if (scale_row % 4 != 0 || !aligned(a.Wsc, 4)) return false;
+    {
+        const int per_row = slab * 2 * ws_bytes / p.scale_gran;
+        int lpr = 1;
+        while (lpr < per_row && lpr < 32) lpr *= 2;
+        p.lanes_per_row = lpr;
+    }
     const size_t stage = (size_t)mma::kRows * (p.pitch_n + p.pitch_s);
-    const size_t red = (size_t)2 * mma::kConsumerWarps * mma::kRows * mma::red_stride(MG) * sizeof(float);
+    const size_t red = (size_t)mma::kConsumerWarps * mma::kRows * mma::red_stride(MG) * sizeof(float);
     const size_t fixed = mma::Smem::kX;
     const size_t xcol = (size_t)MG * mma::kXColBytes;
     const size_t total = (size_t)kMaxDynSmem;
@@ -338,12 +345,13 @@ static bool plan_mma(const GemvArgs& a, int M, int ws_bytes, mma::MmaPlan& p) {
     if (S > 8) S = 8;
     for (; S >= 2; --S)
         if (fixed + align128(xcol * nch) + S * stage + red <= total) break;
+    *whole_k = S >= 2;
     if (S >= 2) {
         p.win_cols = nch;
     } else {
         S = 2;
-        if (fixed + S * stage + red + xcol * slab > total) return false;
-        const size_t avail = total - fixed - S * stage - red;
+        if (fixed + S * stage + red + align128(xcol * slab) > total) return false;
+        const size_t avail = total - fixed - S * stage - red - 128;
         int wc = (int)(avail / xcol) / slab * slab;
         if (wc < slab) return false;
         // equal windows rather than a full one and a sliver
@@ -357,6 +365,24 @@ static bool plan_mma(const GemvArgs& a, int M, int ws_bytes, mma::MmaPlan& p) {
     p.red_off = p.stage_off + (size_t)S * stage;
     p.smem = p.red_off + red;
     return p.smem <= total;
+}
+
+// Decides whether the kernel can take the launch and lays out its shared memory: [barriers, flags | prepared
+// activations (all of K, or a window) | ring of S stages | reduction buffer].  Slabs of 128 columns (2 KB of nibbles
+// per row and copy: the copy engine's request rate favours large copies) where two stages of them fit beside the
+// activations of the whole K, else slabs of 64.
+static bool plan_mma(const GemvArgs& a, int M, int ws_bytes, mma::MmaPlan& p) {
+    const int K = a.K;
+    if (g_tune_force_plain.load() || M < 1 || M > 16 || K % 32 != 0 || a.N < 1) return false;
+    if (!aligned(a.W, 16) || !aligned(a.Wsc, 4) || !aligned(a.x, 16)) return false;
+    if (a.xsc && !aligned(a.xsc, 8)) return false;
+    if (a.x2 && !aligned(a.x2, 16)) return false;
+    if (a.norm_w && !aligned(a.norm_w, 16)) return false;
+    if ((a.xkind == kXHalf) && a.x_stride % 8 != 0) return false;
+    bool whole = false;
+    if (g_tune_mma_slab.load() > 0) return plan_mma_slab(a, M, ws_bytes, g_tune_mma_slab.load(), p, &whole);
+    if (plan_mma_slab(a, M, ws_bytes, 128, p, &whole) && whole) return true;
+    return plan_mma_slab(a, M, ws_bytes, 64, p, &whole);
 }
 
 template <int MG, typename WS>
@@ -389,6 +415,9 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
     if (!aligned(a.W, 8) || !aligned(a.x, 8)) return cudaErrorInvalidValue;
     a.status = status_word_ptr();
     if (!a.status) return cudaErrorInitializationError;
+#ifdef BW_GEMV_TIMELINE
+    a.timeline = g_timeline_ptr;
+#endif
     const bool prequant = (a.xkind == kXInt8 || a.xkind == kXInt4);
     a.nch = a.K / 32;
     if (a.x_stride <= 0) a.x_stride = a.K;
@@ -424,8 +453,7 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
         }
         return cudaSuccess;
     }
-    if (!prequant && M > 8) return cudaErrorInvalidValue;
-    // M > 8: passes of up to 16 (tensor-core streaming kernel) or 8 sequences (pre-quantized operands only).
+    // M > 8: passes of up to 16 (tensor-core streaming kernel) or 8 sequences.
     int pass = 8;
     if (M > 8 && mma_max >= 16) {
         mma::MmaPlan mp;
@@ -437,7 +465,12 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
         b.y = a.y + (size_t)m0 * a.y_stride;
         if (a.residual) b.residual = a.residual + (size_t)m0 * a.y_stride;
         if (a.xkind == kXInt8) b.x = static_cast<const int8_t*>(a.x) + (size_t)m0 * a.K;
-        if (a.xkind == kXInt4) b.x = static_cast<const uint8_t*>(a.x) + (size_t)m0 * (a.K / 2);
+        else if (a.xkind == kXInt4) b.x = static_cast<const uint8_t*>(a.x) + (size_t)m0 * (a.K / 2);
+        else if (a.xkind == kXHalf) b.x = static_cast<const __half*>(a.x) + (size_t)m0 * a.x_stride;
+        else {
+            b.x = static_cast<const float*>(a.x) + (size_t)m0 * a.x_stride;
+            if (a.x2) b.x2 = static_cast<const float*>(a.x2) + (size_t)m0 * a.x_stride;
+        }
         if (a.xsc) b.xsc = a.xsc + (size_t)m0 * (a.K / 16);
         if (mc >= mma_min && mc <= mma_max) {
             mma::MmaPlan mp;
@@ -546,6 +579,20 @@ extern "C" int bw_gemv_int4_fused(float* y_out, const float* x_f32, const float*
     return gemv_dispatch<float>(a, M, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int bw_gemv_int4_decode(float* y_out, long y_stride, const float* residual_or_null, const float* x_f32,
+                                   const float* up_or_null, long x_stride, const float* norm_weight_or_null,
+                                   float eps, const uint8_t* W_packed, const float* W_scale, int K, int N, int M,
+                                   void* stream) {
+    if (up_or_null && norm_weight_or_null) return cudaErrorInvalidValue;
+    GemvArgs a{};
+    a.y = y_out; a.y_stride = y_stride; a.residual = residual_or_null;
+    a.W = W_packed; a.Wsc = W_scale; a.x = x_f32; a.x2 = up_or_null; a.x_stride = x_stride;
+    a.norm_w = norm_weight_or_null; a.eps = eps;
+    a.xkind = up_or_null ? kXSwigluI4 : (norm_weight_or_null ? kXFloatNormI4 : kXFloatI4);
+    a.K = K; a.N = N;
+    return gemv_dispatch<float>(a, M, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int bw_gemv_block_dots(int32_t* dots, const void* x, int a8, const uint8_t* W_packed, int K, int N,
                                   void* stream) {
     if (!dots || !x || !W_packed || K <= 0 || K % 16 != 0 || N < 1) return cudaErrorInvalidValue;
@@ -598,6 +645,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 14: g_tune_mma_max = value; return 0;
         case 15: g_tune_mma_stages = value; return 0;
         case 16: g_tune_shrink_ring = value; return 0;
+        case 17: g_tune_mma_mode = value; return 0;
         default: return cudaErrorInvalidValue;
     }
 }

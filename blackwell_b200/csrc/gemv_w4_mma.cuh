@@ -6,10 +6,12 @@
 //   y[m][n] = sum_kb dot16(W[n,kb], xq[m,kb]) * w_sc[n,kb] * x_sc[m,kb]
 //
 // Work decomposition.  A persistent CTA owns a contiguous range of output rows and walks it in tiles of 32 rows;
-// a tile is streamed in slabs of kSlabCols 32-k columns (1 KB of nibbles per row).  A producer warp (lane = row)
-// issues one bulk copy per row and slab for the nibbles and one for the scales into a ring stage whose row pitch is
-// padded to 16 mod 128 bytes, which makes the ldmatrix reads below conflict-free.  Eight consumer warps split the
-// columns of a slab.  For one column (32 k = two k-blocks) of the 32 rows a warp
+// a tile is streamed in slabs of 32-k columns (1 KB of nibbles per row by default).  Two producer warps fill a ring
+// stage per slab: the nibbles by one bulk copy per row, the scales by cp.async (lanes along a row), both into rows
+// whose pitch is 16 mod 128 bytes, so that the eight rows an ldmatrix or a scale load touches fall into eight
+// different bank groups.
+// Sixteen consumer warps split the columns of a slab.  For one column (32 k = two k-blocks) of the 32
+// rows a warp
 //   * reads the packed nibbles with one ldmatrix.x4: thread (g, t) of the warp gets word t of rows g, g+8, g+16, g+24,
 //   * turns each word into 16*q signed bytes of its even-k and odd-k nibbles (LOP3): exactly the A fragment
 //     {a0, a1, a2, a3} of an m16n8k32 MMA whose k slots are (t, even) and (t, odd),
@@ -19,8 +21,8 @@
 //     bit pattern of 1.5 * 2^23, so the result read as a float is 12582912 + 16 * dot exactly,
 //   * applies the scales with packed fp32 FMAs: t = fma(F, w, -12582912 w) (exact for binary16 w; for fp32 scales
 //     F - 12582912 first), acc = fma(t, x_sc / 16, acc).
-// Each (row, sequence) accumulator lives in exactly one thread of the warp; after the last slab of a tile the eight
-// warps' partial sums are added through shared memory in fixed order (deterministic) and stored.
+// Each (row, sequence) accumulator lives in exactly one thread of the warp; after the last slab of a tile the
+// consumer warps' partial sums are added through shared memory in fixed order (deterministic) and stored.
 //
 // When the prepared activations of all K do not fit beside the ring, K is processed in windows: the CTA prepares a
 // window, runs all its row tiles over the window's slabs and accumulates into y (its rows are its own).
@@ -32,8 +34,11 @@ namespace bw {
 namespace mma {
 
 constexpr int kRows = 32;          // rows per tile
-constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+// Consumer warps per CTA (one more warp produces).  Sixteen: a warp's chain ldmatrix -> unpack -> MMA -> scale FMAs
+// has little instruction-level parallelism, and at HBM speed a 32-row column step may take an SM only ~28 cycles, so
+// the latency has to be covered by many warps.
+constexpr int kConsumerWarps = 16;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;  // + one warp that copies the nibbles, one that copies the scales
 constexpr int kXColBytes = 320;    // prepared activations of one (column, group of 8 sequences): B fragments + scales
 __host__ __device__ constexpr int red_stride(int MG) { return 8 * MG + 1; }  // floats per row of a warp's partial sums (odd: no bank conflicts)
 
@@ -41,9 +46,11 @@ struct MmaPlan {
     int slab_cols;      // 32-k columns per slab
     int win_cols;       // columns per activation window (multiple of slab_cols, or all)
     int S;              // ring stages
-    int pitch_n;        // bytes between rows of a stage: nibbles
-    int pitch_s;        //                                 scales
-    int scale_gran;     // 16: one bulk copy per scale row; 8 or 4: cp.async of that size (rows not 16-byte aligned in HBM)
+    int pitch_n;        // bytes between the nibble rows of a stage
+    int ablate;         // timing experiments: 1 = consumers skip the arithmetic, 2 = the producer copies nothing
+    int pitch_s;        // bytes between the scale rows of a stage
+    int scale_gran;     // size of one cp.async of scales: 16, 8 or 4 bytes (what the rows' alignment in HBM allows)
+    int lanes_per_row;  // producer lanes that share one scale row of a slab (power of two, at most 32)
     size_t x_off, stage_off, red_off, smem;
 };
 
@@ -52,8 +59,8 @@ struct Smem {
     static constexpr int kEmpty = 64;      // S mbarriers
     static constexpr int kAbort = 128;
     static constexpr int kRstd = 192;      // 16 floats
-    static constexpr int kScratch = 256;   // 16 x 8 floats for the norm's block reduction
-    static constexpr int kX = 1024;
+    static constexpr int kScratch = 256;   // 16 sequences x 16 warps floats for the norm's block reduction
+    static constexpr int kX = 2048;
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
@@ -64,8 +71,8 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
 // D = A (16 x 32, s8) * B (32 x 8, s8) + C, int32.
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1, int c) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+    // not volatile: a pure function of its register operands, free to be scheduled around the loads of the next column
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
 }
@@ -76,6 +83,9 @@ __device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, 
     asm("mov.b64 %0, {%1, %2};" : "=l"(C) : "f"(c0), "f"(c1));
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(D) : "l"(A), "l"(B), "l"(C));
     asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(D));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
@@ -112,8 +122,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
     unsigned char* xbase = smem + p.x_off;
     unsigned char* stages = smem + p.stage_off;
     float* red = reinterpret_cast<float*>(smem + p.red_off);
-    const size_t stage_bytes = (size_t)kRows * (p.pitch_n + p.pitch_s);
     const size_t stage_sc = (size_t)kRows * p.pitch_n;  // scales follow the nibbles inside a stage
+    const size_t stage_bytes = stage_sc + (size_t)kRows * p.pitch_s;
 
     // this CTA's rows
     const int row_begin = (int)(((long long)a.N * blockIdx.x) / gridDim.x);
@@ -122,9 +132,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
     const int nwin = (nch + p.win_cols - 1) / p.win_cols;
 
     if (t == 0) {
-        // full: one arrive.expect_tx by the producer's lane 0, plus (unaligned scale rows) one cp.async arrival per lane
+        // full: the arrive.expect_tx of the producer's lane 0 (nibbles) and one arrival per producer lane, made by the
+        // hardware when the lane's cp.async copies (scales) have landed
         for (int s = 0; s < S; ++s) {
-            mbar_init(smem_u32(&full[s]), p.scale_gran == 16 ? 1 : 33);
+            mbar_init(smem_u32(&full[s]), 33);
             mbar_init(smem_u32(&empty[s]), kConsumerWarps);
         }
         *abort_flag = 0;
@@ -133,10 +144,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
     __syncthreads();
     pdl_trigger();
 
-    if (warp == kConsumerWarps) {
-        // ------------------------------------------------------------------ producer: lane = row of the tile
-        const uint64_t policy = l2_policy_evict_first();
+    if (warp >= kConsumerWarps) {
+        // ------------------------------------------------------------------ producers
+        // Warp 16 copies the nibbles (one bulk copy per row, lane = row), warp 17 the scales (cp.async, lanes along a
+        // row): two warps because each works through its copies one instruction after the other, and together they
+        // would take longer than a slab lasts at HBM speed.
+        const bool nib_warp = warp == kConsumerWarps;
         const int ws = (int)sizeof(WS);
+        const uint64_t policy = l2_policy_evict_first();
         int item = 0;
         bool ok = true;
         for (int w = 0; w < nwin && ok; ++w) {
@@ -152,30 +167,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
                     }
                     if (*abort_flag) { ok = false; break; }
                     const uint32_t fb = smem_u32(&full[s]);
-                    const uint32_t nb = (uint32_t)cols * 16u, sb = (uint32_t)cols * 2u * ws;
-                    if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows * (nb + (p.scale_gran == 16 ? sb : 0u)));
-                    __syncwarp();
                     unsigned char* st = stages + (size_t)s * stage_bytes;
-                    if (lane < rows) {
-                        const size_t grow = (size_t)(r0 + lane);
-                        bulk_g2s(smem_u32(st + (size_t)lane * p.pitch_n), a.W + grow * (size_t)(K / 2) + (size_t)c0 * 16, nb,
-                                 fb, policy);
-                        const unsigned char* ssrc = static_cast<const unsigned char*>(a.Wsc) +
-                                                    (grow * (size_t)(K / 16) + (size_t)c0 * 2) * ws;
-                        unsigned char* sdst = st + stage_sc + (size_t)lane * p.pitch_s;
-                        if (p.scale_gran == 16) {
-                            bulk_g2s(smem_u32(sdst), ssrc, sb, fb, policy);
-                        } else if (p.scale_gran == 8) {
-                            for (uint32_t o = 0; o < sb; o += 8) cp_async8(smem_u32(sdst + o), ssrc + o);
-                        } else {
-                            for (uint32_t o = 0; o < sb; o += 4) cp_async4(smem_u32(sdst + o), ssrc + o);
+                    if (nib_warp) {
+                        const uint32_t nb = (p.ablate & 2) ? 0u : (uint32_t)cols * 16u;
+                        if (lane == 0) mbar_expect_tx(fb, (uint32_t)rows * nb);
+                        __syncwarp();
+                        if (lane < rows && nb)
+                            bulk_g2s(smem_u32(st + (size_t)lane * p.pitch_n),
+                                     a.W + (size_t)(r0 + lane) * (size_t)(K / 2) + (size_t)c0 * 16, nb, fb, policy);
+                        continue;
+                    }
+                    // scales: `lpr` lanes run along a row (coalesced), `gran` bytes per copy, 32 / lpr rows per pass
+                    const uint32_t sb = (uint32_t)cols * 2u * ws;      // bytes per row in this slab
+                    const uint32_t per_row = (p.ablate & 2) ? 0u : sb / (uint32_t)p.scale_gran;
+                    const unsigned char* sbase = static_cast<const unsigned char*>(a.Wsc) +
+                                                 ((size_t)r0 * (size_t)(K / 16) + (size_t)c0 * 2) * ws;
+                    const size_t srow = (size_t)(K / 16) * ws;
+                    const uint32_t lpr = (uint32_t)p.lanes_per_row, rstep = 32u / lpr;
+                    const uint32_t dbase = smem_u32(st + stage_sc);
+                    for (uint32_t oi = lane & (lpr - 1u); oi < per_row; oi += lpr) {
+                        const uint32_t o = oi * (uint32_t)p.scale_gran;
+                        uint32_t rr = lane / lpr;  // lpr is a power of two
+                        uint32_t dst = dbase + rr * (uint32_t)p.pitch_s + o;
+                        const unsigned char* src = sbase + (size_t)rr * srow + o;
+                        for (; rr < (uint32_t)rows; rr += rstep, dst += rstep * (uint32_t)p.pitch_s, src += rstep * srow) {
+                            if (p.scale_gran == 16) cp_async16(dst, src);
+                            else if (p.scale_gran == 8) cp_async8(dst, src);
+                            else cp_async4(dst, src);
                         }
                     }
-                    if (p.scale_gran != 16) cp_async_arrive_noinc(fb);
+                    cp_async_arrive_noinc(fb);
                 }
             }
         }
-        if (p.scale_gran != 16) asm volatile("cp.async.wait_all;" ::: "memory");
+        if (!nib_warp) asm volatile("cp.async.wait_all;" ::: "memory");
         return;
     }
 
@@ -187,7 +212,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
     float acc[2][2][MG][2];  // [row group][row g / g+8][sequence group][sequence 2t / 2t+1]
     int item = 0;
     bool ok = true;
-    int tile_count = 0;
 
     for (int w = 0; w < nwin; ++w) {
         const int wc0 = w * p.win_cols, wc1 = min(nch, wc0 + p.win_cols);
@@ -235,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
             consumer_sync();
         }
 
-        for (int tile = 0; tile < ntiles; ++tile, ++tile_count) {
+        for (int tile = 0; tile < ntiles; ++tile) {
             const int r0 = row_begin + tile * kRows;
             const int rows = min(kRows, row_end - r0);
 #pragma unroll
@@ -249,14 +273,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
                 const int cols = min(p.slab_cols, wc1 - c0);
                 const int s = item % S;
                 if (ok && !mbar_wait(smem_u32(&full[s]), (item / S) & 1)) { *abort_flag = 1; ok = false; }
-                if (ok) {
+                if (ok && !(p.ablate & 1)) {
                     const unsigned char* st = stages + (size_t)s * stage_bytes;
-                    const uint32_t st_n = smem_u32(st) + (uint32_t)lane * p.pitch_n;
+                    const uint32_t st_n = smem_u32(st) + (uint32_t)lane * (uint32_t)p.pitch_n;
                     const unsigned char* st_s = st + stage_sc + (size_t)g * p.pitch_s;
-#pragma unroll 2
+#pragma unroll 4
                     for (int cl = warp; cl < cols; cl += kConsumerWarps) {
                         uint32_t r[4];
-                        ldmatrix_x4(st_n + 16u * cl, r);
+                        ldmatrix_x4(st_n + 16u * (uint32_t)cl, r);
                         uint32_t lo[4], hi[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) nibbles_to_s8x16(r[j], lo[j], hi[j]);
@@ -302,10 +326,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
                 if (lane == 0) mbar_arrive(smem_u32(&empty[s]));  // this warp is done with the stage
             }
 
-            // ---- the eight warps' partial sums of the tile -> y
+            // ---- the consumer warps' partial sums of the tile -> y (fixed order: deterministic)
             constexpr int RS = red_stride(MG);
-            float* rb = red + (size_t)(tile_count & 1) * (kConsumerWarps * kRows * RS);
-            float* mine = rb + (size_t)warp * (kRows * RS);
+            float* mine = red + (size_t)warp * (kRows * RS);
 #pragma unroll
             for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -324,13 +347,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
                     if (row < rows && m < M) {
                         float sum = 0.f;
 #pragma unroll
-                        for (int wv = 0; wv < kConsumerWarps; ++wv) sum += rb[(size_t)wv * (kRows * RS) + row * RS + m];
+                        for (int wv = 0; wv < kConsumerWarps; ++wv) sum += red[(size_t)wv * (kRows * RS) + row * RS + m];
                         const size_t yi = (size_t)m * a.y_stride + r0 + row;
                         if (w == 0) a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
                         else a.y[yi] += sum;
                     }
                 }
             }
+            consumer_sync();  // the buffer is free for the next tile's partial sums
         }
     }
     if (!ok && ct == 0) {

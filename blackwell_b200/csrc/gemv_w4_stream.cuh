@@ -53,6 +53,9 @@ struct GemvArgs {
     const float* norm_w;    // [K] for kXFloatNorm
     const float* residual;  // optional [M][y_stride]: added to the result (may alias y)
     int* status;            // device status word (bw_device_status)
+#ifdef BW_GEMV_TIMELINE
+    unsigned long long* timeline;  // experiment builds only: per-phase %globaltimer stamps of a few CTAs
+#endif
     long x_stride;          // elements between sequences of x / x2 (f16 and f32 kinds)
     long y_stride;          // elements between sequences of y and residual
     float eps;
@@ -73,6 +76,7 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], uint32_t (&
 #pragma unroll
     for (int i = 0; i < 16; ++i) am = fmaxf(am, fabsf(v[i]));
     const float sc = kInt4Rule ? quant_scale_i4(am) : quant_scale_i8(am);
+    const float rcp = 1.0f / sc;
     s = sc * 0.0625f;
 #pragma unroll
     for (int wd = 0; wd < 2; ++wd) {
@@ -80,8 +84,8 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], uint32_t (&
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float ve = v[8 * wd + 2 * j], vo = v[8 * wd + 2 * j + 1];
-            const int qe = kInt4Rule ? quant_i4(ve, sc) : quant_i8(ve, sc);
-            const int qo = kInt4Rule ? quant_i4(vo, sc) : quant_i8(vo, sc);
+            const int qe = kInt4Rule ? quant_i4(ve, sc, rcp) : quant_i8(ve, sc, rcp);
+            const int qo = kInt4Rule ? quant_i4(vo, sc, rcp) : quant_i8(vo, sc, rcp);
             ee |= (uint32_t)(qe & 0xFF) << (8 * j);
             oo |= (uint32_t)(qo & 0xFF) << (8 * j);
         }
@@ -280,6 +284,21 @@ gemv_w4_stream_kernel(const GemvArgs a) {
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int T = blockDim.x;
     const int K = a.K, nch = a.nch, Tg = a.Tg, G = a.G, S = a.S;
+#ifdef BW_GEMV_TIMELINE
+    unsigned long long*& tl_base = *reinterpret_cast<unsigned long long**>(smem + 80);
+    if (t == 0) {
+        tl_base = nullptr;
+        const int sel = blockIdx.x == 0 ? 0 : (blockIdx.x == gridDim.x / 2 ? 1 : (blockIdx.x == gridDim.x - 1 ? 2 : -1));
+        if (a.timeline && sel >= 0) {
+            unsigned long long li = sel == 0 ? atomicAdd(a.timeline, 1ull) : a.timeline[0];
+            tl_base = a.timeline + 16 + (li % 32) * 48 + sel * 16;
+            tl_base[0] = global_ns();
+        }
+    }
+#define BW_TL(i) do { if (t == 0 && tl_base) tl_base[i] = global_ns(); } while (0)
+#else
+#define BW_TL(i) do { } while (0)
+#endif
     const int R = a.rg * G;  // rows per tile; a.rg <= RG
     const int g = t / Tg, tg = t - g * Tg;
     const int warps_per_group = Tg >> 5;
@@ -328,8 +347,10 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         for (int i = 0; i < pre; ++i) issue_tile(i);
     }
     // The weights never depend on the previous kernel, the activations and y do: only now wait for it.
+    BW_TL(1);
     pdl_trigger();
     pdl_wait();
+    BW_TL(2);
 
     // ---- activation prologue (overlaps the first weight tiles in flight) ----
     const bool needs_norm = (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4);
@@ -387,6 +408,7 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         }
     };
     if (!kMultiPass && tg < nch) load_x(tg);
+    BW_TL(3);
 
     // ------------------------------------------------------------- main loop
     bool aborted = false;
@@ -394,6 +416,7 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         const int s = tile % S;
         const uint32_t parity = (uint32_t)(tile / S) & 1u;
         if (!mbar_wait(smem_u32(&bars[s]), parity)) *abort_flag = 1;
+        if (tile == 0) BW_TL(4);
 
         const unsigned char* st = stages + (size_t)s * stage_bytes;
         const int r0 = row_begin + tile * R;
@@ -415,6 +438,7 @@ gemv_w4_stream_kernel(const GemvArgs a) {
             }
         }
 
+        if (tile == 0) BW_TL(5);
         // warp totals of the V = RG*M partial sums, one value index per lane group
         const float tot = warp_sum_many<V>(acc, lane);
         constexpr int P = V <= 1 ? 1 : V <= 2 ? 2 : V <= 4 ? 4 : V <= 8 ? 8 : V <= 16 ? 16 : 32;
@@ -440,6 +464,7 @@ gemv_w4_stream_kernel(const GemvArgs a) {
         }
     }
 
+    BW_TL(6);
     if (aborted && t == 0) {
         // Give copies still in flight a bounded chance to land before the CTA's
         // shared memory is released, then report.

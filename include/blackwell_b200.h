@@ -86,6 +86,12 @@ int bw_gemv_w4a8_decode(float* y_out, long y_stride, const float* residual_or_nu
 int bw_gemv_int4_fused(float* y_out, const float* x_f32, const float* up_or_null, const float* norm_weight_or_null,
                        float eps, const uint8_t* W_packed, const float* W_scale, int K, int N, int M, void* stream);
 
+/* The same reference-format GEMV as the decode step uses it: row strides and an optional residual, as
+ * bw_gemv_w4a8_decode.  Any M. */
+int bw_gemv_int4_decode(float* y_out, long y_stride, const float* residual_or_null, const float* x_f32,
+                        const float* up_or_null, long x_stride, const float* norm_weight_or_null, float eps,
+                        const uint8_t* W_packed, const float* W_scale, int K, int N, int M, void* stream);
+
 /* Debug/inspection: per-block integer dot products of one sequence,
  * dots i32 [N][K/16], produced by the same unpack + dp4a code as the GEMVs.
  * x is INT4-packed (a8 == 0) or int8 (a8 != 0). */
@@ -167,6 +173,19 @@ int bw_qk_norm_rope_kv_f16(float* q_out, uint16_t* k_cache, uint16_t* v_cache, c
  * copy (server/inference_server_int4_batched.cu:251), token ids read from device memory.  H % 8 == 0. */
 int bw_embed_gather_f16(float* x_out, const uint16_t* table_f16, const int* d_tokens, int H, int vocab, int M,
                         void* stream);
+/* The same lookup from an fp32 table (the form the reference keeps its dequantized embedding in,
+ * server/inference_server_int4_batched.cu:196-217).  H % 4 == 0. */
+int bw_embed_gather_f32(float* x_out, const float* table_f32, const int* d_tokens, int H, int vocab, int M,
+                        void* stream);
+/* Token bookkeeping of a batched generation that stays on the GPU (the reference decides on the host, one sequence at
+ * a time: server/inference_server_int4_batched.cu:248-250, 295-299).  Sequence m consumes, at position
+ * d_seq_pos[m], the id prompt[m][pos] while pos < prompt_len[m] and the previously sampled id afterwards
+ * (bw_select_input_tokens); after sampling has advanced the position to p, a token beyond the prompt is stored as
+ * generated token p - prompt_len[m] of gen i32 [M][max_new] (bw_record_generated). */
+int bw_select_input_tokens(int* tokens_in, const int* sampled, const int* prompt, const int* prompt_len,
+                           const int* d_seq_pos, int M, int max_prompt, void* stream);
+int bw_record_generated(int* gen, const int* sampled, const int* prompt_len, const int* d_seq_pos, int M, int max_new,
+                        void* stream);
 /* Greedy argmax of each row of logits f32 [M][row_stride] (rule of sample_argmax_gpu,
  * src/kernels/sample_gpu.cu:30-60) into out_ids[M]; when seq_pos_to_advance is not NULL each of its M entries
  * is incremented, which closes a decode step inside a CUDA graph -- but never beyond pos_limit (pass
@@ -245,6 +264,41 @@ int bw_w4_file_upload(const char* prefix, int want_f32_scales, int want_f16_scal
 int bw_w4_free(bw_dev_w4* w);
 int bw_f32_file_write(const char* path, const float* data, size_t n);
 int bw_f32_file_read(const char* path, float* data_out, size_t n);
+
+/* ---- Batched decode-step driver ----
+ * The host side of the INT4 servers' token loop above the kernel entry points: it mirrors the per-layer sequence of
+ * server/inference_server_int4_batched.cu:253-298 and the captured-graph form of
+ * bench/decode_int4_cgraph_8b.cu:249-399 (capture :268, instantiate :332, launch :347) for a whole batch with
+ * per-sequence positions.  bw_decode_create loads a weight directory in the reference's container format (the file
+ * names of load_model, server/inference_server_int4_batched.cu:150-184), allocates a binary16 KV cache of
+ * batch x max_seq positions, runs one step eagerly (which sizes the library's scratch memory) and captures the step
+ * in a CUDA graph (use_graph != 0); it synchronises and allocates, the calls after it do neither except where
+ * stated.  act_bits 8: int8 activations, binary16 weight scales (the fast path); act_bits 4: the reference's own
+ * arithmetic (quantize_int4 rule, fp32 weight scales).
+ * A generation: bw_decode_begin uploads prompt_ids i32 [batch][max_prompt] and prompt_len[batch] (host memory;
+ * 1 <= len <= max_prompt <= cfg.max_prompt), resets the positions to 0 and synchronises the stream; every
+ * bw_decode_step then advances all sequences by one token (it feeds the prompt while it lasts, then the sampled
+ * ids, greedy) with no host decision -- max(prompt_len) + max_new - 1 steps complete the longest sequence;
+ * bw_decode_result copies gen i32 [batch][cfg.max_new] to the host (-1 = not generated) and synchronises.
+ * bw_decode_buffers exposes the device buffers (logits f32 [batch][vocab], hidden state, positions, sampled ids,
+ * caches [batch][layers][kv_heads][max_seq][128]) for inspection.  One stream at a time per engine. */
+typedef struct bw_decode bw_decode;
+typedef struct bw_decode_config {
+    int layers, hidden, inter, n_q_heads, n_kv_heads, head_dim, vocab;
+    float eps, rope_base;
+    int batch, max_seq;       /* sequences per step; cache positions per sequence */
+    int max_prompt, max_new;  /* capacity of the device-side prompt and result tables */
+    int act_bits;             /* 8 or 4 */
+    int use_graph;            /* capture the step once and replay it */
+    const char* weights_dir;  /* read during bw_decode_create only */
+} bw_decode_config;
+int bw_decode_create(const bw_decode_config* cfg, bw_decode** out);
+int bw_decode_begin(bw_decode* d, const int* prompt_ids, const int* prompt_len, int max_prompt, void* stream);
+int bw_decode_step(bw_decode* d, void* stream);
+int bw_decode_result(bw_decode* d, int* gen_out, void* stream);
+int bw_decode_buffers(bw_decode* d, float** logits, float** hidden, int** positions, int** sampled,
+                      uint16_t** k_cache, uint16_t** v_cache);
+int bw_decode_destroy(bw_decode* d);
 
 /* ---- Tensor-parallel exchange over peer memory (no counterpart in the reference, which is single-GPU) ----
  * All-reduce of the K-split projections' partial sums across the GPUs of one box through NVLink peer loads.
