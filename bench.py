@@ -298,7 +298,7 @@ def run_ours(args, rank, world, local_rank):
     p1.record()
     torch.cuda.synchronize()
     est = max(p0.elapsed_time(p1) / 10 / 1e3, 1e-6)
-    passes = max(1, int(np.ceil(MIN_TIMED_SECONDS / (est * args.steps))))
+    passes = max(1, int(np.ceil(args.min_time / (est * args.steps))))
     if world > 1:
         pt = torch.tensor([passes], dtype=torch.int64, device=dev)
         dist.all_reduce(pt, op=dist.ReduceOp.MAX)
@@ -812,6 +812,8 @@ def main():
                     "BATCH:CTX:NQH:NKV on a synthetic cache; prints its own JSON line")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="N > 1: how the K-split partial sums "
                     "are summed across ranks (library NVLink peer-load all-reduce, or NCCL)")
+    ap.add_argument("--min-time", type=float, default=MIN_TIMED_SECONDS, help="shortest timed region in seconds (each "
+                    "step is timed as the mean of as many passes as that needs); 0 for profiling runs")
     ap.add_argument("--tune", default=None, help="profiling aid: comma list of key=value for bw_set_tuning")
     args = ap.parse_args()
     global _ONLY

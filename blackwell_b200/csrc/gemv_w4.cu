@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(128) block_dots_kernel(int32_t* dots, const ui
 static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0}, g_tune_rg{0}, g_tune_threads{0}, g_tune_tc_min{0};
 static std::atomic<int> g_tune_shrink_ring{1};
 static std::atomic<int> g_tune_mma_mode{0};
+static std::atomic<int> g_tune_mma_pack{1};
 #ifdef BW_GEMV_TIMELINE
 static unsigned long long* g_timeline_ptr = nullptr;
 extern "C" void bw_debug_set_timeline(void* dev_ptr) { g_timeline_ptr = static_cast<unsigned long long*>(dev_ptr); }
@@ -385,9 +386,9 @@ static bool plan_mma(const GemvArgs& a, int M, int ws_bytes, mma::MmaPlan& p) {
     return plan_mma_slab(a, M, ws_bytes, 64, p, &whole);
 }
 
-template <int MG, typename WS>
+template <int MG, typename WS, bool kPack>
 static cudaError_t launch_mma_inst(const GemvArgs& a, const mma::MmaPlan& p, int M, cudaStream_t st) {
-    auto kern = mma::gemv_w4_mma_kernel<MG, WS>;
+    auto kern = mma::gemv_w4_mma_kernel<MG, WS, kPack>;
     static std::once_flag once[kMaxDevices];
     const int dev = current_device();
     cudaError_t attr_err = cudaSuccess;
@@ -405,7 +406,8 @@ static cudaError_t launch_mma_inst(const GemvArgs& a, const mma::MmaPlan& p, int
 
 template <typename WS>
 static cudaError_t launch_mma(const GemvArgs& a, const mma::MmaPlan& p, int M, cudaStream_t st) {
-    return M <= 8 ? launch_mma_inst<1, WS>(a, p, M, st) : launch_mma_inst<2, WS>(a, p, M, st);
+    if (M <= 4 && g_tune_mma_pack.load() != 0) return launch_mma_inst<1, WS, true>(a, p, M, st);
+    return M <= 8 ? launch_mma_inst<1, WS, false>(a, p, M, st) : launch_mma_inst<2, WS, false>(a, p, M, st);
 }
 
 template <typename WS>
@@ -424,12 +426,19 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
     if (a.y_stride <= 0) a.y_stride = a.N;
     if (a.x_stride % 4 != 0 || a.y_stride < a.N) return cudaErrorInvalidValue;
     if (!prequant && !aligned(a.x, 16)) return cudaErrorInvalidValue;
-    // 3..16 sequences: the streaming kernel with warp-level tensor-core dots, either scale type.
-    const int mma_min = g_tune_mma_min.load() > 0 ? g_tune_mma_min.load() : 3;
+    // 5..16 sequences: the streaming kernel with warp-level tensor-core dots, either scale type (routing by
+    // measurement: up to 4 sequences the dp4a kernel is as fast or faster; from 9 sequences on, shapes whose prepared
+    // activations need several windows of K are faster on the tcgen05 kernel).
+    const int mma_min = g_tune_mma_min.load() > 0 ? g_tune_mma_min.load() : 5;
     const int mma_max = g_tune_mma_max.load() > 0 ? g_tune_mma_max.load() : 16;
     if (M >= mma_min && M <= mma_max && M <= 16) {
         mma::MmaPlan mp;
-        if (plan_mma(a, M, (int)sizeof(WS), mp)) return launch_mma<WS>(a, mp, M, st);
+        if (plan_mma(a, M, (int)sizeof(WS), mp)) {
+            const bool windows = mp.win_cols < a.K / 32;
+            const bool tc_can = sizeof(WS) == 2 && M > 8 && tc::eligible(a, M);
+            const bool forced = g_tune_mma_min.load() > 0;  // an explicit range (tests, experiments) takes the kernel as it is
+            if (forced || !(windows && tc_can)) return launch_mma<WS>(a, mp, M, st);
+        }
     }
     // Larger batches go to the tcgen05 kernel, up to 64 sequences per launch.
     const int tc_min = g_tune_tc_min.load() > 0 ? g_tune_tc_min.load() : 8;
@@ -646,6 +655,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 15: g_tune_mma_stages = value; return 0;
         case 16: g_tune_shrink_ring = value; return 0;
         case 17: g_tune_mma_mode = value; return 0;
+        case 18: g_tune_mma_pack = value; return 0;
         default: return cudaErrorInvalidValue;
     }
 }

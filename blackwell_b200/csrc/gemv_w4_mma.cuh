@@ -108,9 +108,13 @@ template <> struct ScalePairF<float> {
     static __device__ __forceinline__ float2 load(const unsigned char* p) { return *reinterpret_cast<const float2*>(p); }
 };
 
-// MG groups of 8 sequences (M <= 8 MG); WS = weight scale type.
-template <int MG, typename WS>
+// MG groups of 8 sequences (M <= 8 MG); WS = weight scale type.  kPack (MG = 1, M <= 4): the eight B columns of one MMA
+// are the four sequences against the first k-block (other half of K zero) and the same four against the second, so
+// ONE instruction per 16 rows yields both blocks' dots; the accumulators of the two blocks of a (row, sequence) then
+// sit in two threads and meet in the cross-warp sum.
+template <int MG, typename WS, bool kPack>
 __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs a, const MmaPlan p, int M) {
+    static_assert(!kPack || MG == 1, "packing is for one group of sequences");
     extern __shared__ __align__(128) unsigned char smem[];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int K = a.K, nch = a.nch, S = p.S;
@@ -239,22 +243,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
         }
         {
             const int wcols = wc1 - wc0;
-            const int nblk = 2 * wcols * 8 * MG;  // (column, block of the column, sequence)
+            constexpr int SEQ = kPack ? 4 : 8 * MG;  // sequence slots per column
+            const int nblk = 2 * wcols * SEQ;        // (column, block of the column, sequence)
             for (int idx = ct; idx < nblk; idx += kConsumerWarps * 32) {
-                const int m = idx % (8 * MG);
-                const int cb = idx / (8 * MG);
+                const int m = idx % SEQ;
+                const int cb = idx / SEQ;
                 const int cl = cb >> 1, blk = cb & 1;
                 uint32_t e[2] = {0u, 0u}, o[2] = {0u, 0u};
                 float sc = 0.f;
                 if (m < M) make_xblock(a, m, 2 * (wc0 + cl) + blk, needs_norm ? rstd_s[m] : 1.f, e, o, sc);
-                unsigned char* xc = xbase + ((size_t)cl * MG + (m >> 3)) * kXColBytes;
-                // lanes (g = m % 8, t = 2 blk) and (g, 2 blk + 1): {even-k bytes, odd-k bytes} of the block's two words
-                uint2* bf = reinterpret_cast<uint2*>(xc) + (m & 7) * 4 + 2 * blk;
-                bf[0] = make_uint2(e[0], o[0]);
-                bf[1] = make_uint2(e[1], o[1]);
-                // scales: per pair of sequences (2t, 2t+1): {A 2t, A 2t+1, B 2t, B 2t+1}
-                float* sf = reinterpret_cast<float*>(xc + 256) + ((m & 7) >> 1) * 4 + 2 * blk + (m & 1);
-                *sf = sc;
+                if (kPack) {
+                    // B column g = m + 4 blk: the block's two words in the k slots of lanes t = 2 blk, 2 blk + 1, zeros in
+                    // the other two; scales: thread t reads {sequence 2 (t & 1), 2 (t & 1) + 1} of block t >> 1
+                    unsigned char* xc = xbase + (size_t)cl * kXColBytes;
+                    uint2* bf = reinterpret_cast<uint2*>(xc) + (m + 4 * blk) * 4;
+                    bf[2 * blk] = make_uint2(e[0], o[0]);
+                    bf[2 * blk + 1] = make_uint2(e[1], o[1]);
+                    bf[2 * (1 - blk)] = make_uint2(0u, 0u);
+                    bf[2 * (1 - blk) + 1] = make_uint2(0u, 0u);
+                    reinterpret_cast<float*>(xc + 256)[(2 * blk + (m >> 1)) * 2 + (m & 1)] = sc;
+                } else {
+                    unsigned char* xc = xbase + ((size_t)cl * MG + (m >> 3)) * kXColBytes;
+                    // lanes (g = m % 8, t = 2 blk) and (g, 2 blk + 1): {even-k bytes, odd-k bytes} of the block's two words
+                    uint2* bf = reinterpret_cast<uint2*>(xc) + (m & 7) * 4 + 2 * blk;
+                    bf[0] = make_uint2(e[0], o[0]);
+                    bf[1] = make_uint2(e[1], o[1]);
+                    // scales: per pair of sequences (2t, 2t+1): {A 2t, A 2t+1, B 2t, B 2t+1}
+                    float* sf = reinterpret_cast<float*>(xc + 256) + ((m & 7) >> 1) * 4 + 2 * blk + (m & 1);
+                    *sf = sc;
+                }
             }
             consumer_sync();
         }
@@ -289,6 +306,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
                         for (int j = 0; j < 4; ++j)
                             wsc[j] = ScalePairF<WS>::load(st_s + (size_t)(8 * j) * p.pitch_s + (size_t)cl * (2 * sizeof(WS)));
                         const unsigned char* xc = xbase + (size_t)(c0 - wc0 + cl) * MG * kXColBytes;
+                        if constexpr (kPack) {
+                            const uint2 bf = *reinterpret_cast<const uint2*>(xc + lane * 8);
+                            const float2 xs = *reinterpret_cast<const float2*>(xc + 256 + tq * 8);
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                int d[4];
+                                mma_s8(d, lo[2 * i], lo[2 * i + 1], hi[2 * i], hi[2 * i + 1], bf.x, bf.y, kMagicInt);
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    const float2 w2 = wsc[2 * i + h];
+                                    const float w = tq < 2 ? w2.x : w2.y;  // this thread's columns belong to one block
+                                    float t0, t1;
+                                    if (sizeof(WS) == 2) {
+                                        const float cw = -kMagicFloat * w;  // exact
+                                        t0 = fmaf(__int_as_float(d[2 * h]), w, cw);
+                                        t1 = fmaf(__int_as_float(d[2 * h + 1]), w, cw);
+                                    } else {
+                                        t0 = (__int_as_float(d[2 * h]) - kMagicFloat) * w;
+                                        t1 = (__int_as_float(d[2 * h + 1]) - kMagicFloat) * w;
+                                    }
+                                    ffma2(acc[i][h][0][0], acc[i][h][0][1], t0, t1, xs.x, xs.y, acc[i][h][0][0], acc[i][h][0][1]);
+                                }
+                            }
+                        } else {
 #pragma unroll
                         for (int c = 0; c < MG; ++c) {
                             const uint2 bf = *reinterpret_cast<const uint2*>(xc + c * kXColBytes + lane * 8);
@@ -306,9 +347,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
                                     const float2 w2 = wsc[2 * i + h];
                                     float tA0, tA1, tB0, tB1;
                                     if (sizeof(WS) == 2) {
+                                        // scalar here (a packed FMA would need w and c duplicated into register pairs),
+                                        // packed below where all three operands already sit in pairs
                                         const float cA = -kMagicFloat * w2.x, cB = -kMagicFloat * w2.y;  // exact
-                                        ffma2(tA0, tA1, __int_as_float(dA[2 * h]), __int_as_float(dA[2 * h + 1]), w2.x, w2.x, cA, cA);
-                                        ffma2(tB0, tB1, __int_as_float(dB[2 * h]), __int_as_float(dB[2 * h + 1]), w2.y, w2.y, cB, cB);
+                                        tA0 = fmaf(__int_as_float(dA[2 * h]), w2.x, cA);
+                                        tA1 = fmaf(__int_as_float(dA[2 * h + 1]), w2.x, cA);
+                                        tB0 = fmaf(__int_as_float(dB[2 * h]), w2.y, cB);
+                                        tB1 = fmaf(__int_as_float(dB[2 * h + 1]), w2.y, cB);
                                     } else {
                                         tA0 = (__int_as_float(dA[2 * h]) - kMagicFloat) * w2.x;
                                         tA1 = (__int_as_float(dA[2 * h + 1]) - kMagicFloat) * w2.x;
@@ -319,6 +364,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
                                     ffma2(acc[i][h][c][0], acc[i][h][c][1], tB0, tB1, xs.z, xs.w, acc[i][h][c][0], acc[i][h][c][1]);
                                 }
                             }
+                        }
                         }
                     }
                 }
@@ -342,12 +388,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
             consumer_sync();
             if (*abort_flag) ok = false;
             if (ok) {
-                for (int o = ct; o < kRows * 8 * MG; o += kConsumerWarps * 32) {
+                for (int o = ct; o < kRows * (kPack ? 4 : 8 * MG); o += kConsumerWarps * 32) {
                     const int row = o & (kRows - 1), m = o >> 5;
                     if (row < rows && m < M) {
                         float sum = 0.f;
 #pragma unroll
-                        for (int wv = 0; wv < kConsumerWarps; ++wv) sum += red[(size_t)wv * (kRows * RS) + row * RS + m];
+                        for (int wv = 0; wv < kConsumerWarps; ++wv) {
+                            const float* rp = red + (size_t)wv * (kRows * RS) + row * RS + m;
+                            sum += kPack ? rp[0] + rp[4] : rp[0];  // packed: first block's column + second block's
+                        }
                         const size_t yi = (size_t)m * a.y_stride + r0 + row;
                         if (w == 0) a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
                         else a.y[yi] += sum;

@@ -69,7 +69,12 @@ struct GemvArgs {
     int rg;                 // rows per group in one tile (<= RowsPerGroup<M>)
 };
 
-// 16 floats (one k-block) -> signed bytes in nibble order + scale/16.
+// 16 floats (one k-block) -> signed bytes in nibble order + scale/16, with the reference's bits (q = roundf(v / sc),
+// IEEE division, ties away from zero).  The common path avoids the sixteen divisions and roundf sequences: with
+// rcp = 1 / sc, v * rcp lies within 1.6e-5 of the true quotient (|v / sc| <= 127), so rint(v * rcp) is the reference's
+// integer unless that product sits within 3e-5 of a half; a block with such an element (about one in a thousand), or
+// with a non-finite value, is redone with the reference's own formula.  No clamp is needed on the common path: sc is
+// absmax / 127 (or / 7), which bounds |v * rcp| by 127.0001 (7.000001).
 template <bool kInt4Rule>
 __device__ __forceinline__ void quantize_block(const float (&v)[16], uint32_t (&e)[2], uint32_t (&o)[2], float& s) {
     float am = 0.f;
@@ -78,16 +83,26 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], uint32_t (&
     const float sc = kInt4Rule ? quant_scale_i4(am) : quant_scale_i8(am);
     const float rcp = 1.0f / sc;
     s = sc * 0.0625f;
+    int q[16];
+    bool exact_needed = !(am < 3.0e38f);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float r = v[i] * rcp;
+        const float ri = rintf(r);
+        exact_needed |= !(fabsf(fabsf(r - ri) - 0.5f) > 3e-5f);  // also true for a NaN
+        q[i] = (int)ri;
+    }
+    if (exact_needed) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) q[i] = kInt4Rule ? quant_i4(v[i], sc) : quant_i8(v[i], sc);
+    }
 #pragma unroll
     for (int wd = 0; wd < 2; ++wd) {
         uint32_t ee = 0, oo = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float ve = v[8 * wd + 2 * j], vo = v[8 * wd + 2 * j + 1];
-            const int qe = kInt4Rule ? quant_i4(ve, sc, rcp) : quant_i8(ve, sc, rcp);
-            const int qo = kInt4Rule ? quant_i4(vo, sc, rcp) : quant_i8(vo, sc, rcp);
-            ee |= (uint32_t)(qe & 0xFF) << (8 * j);
-            oo |= (uint32_t)(qo & 0xFF) << (8 * j);
+            ee |= (uint32_t)(q[8 * wd + 2 * j] & 0xFF) << (8 * j);
+            oo |= (uint32_t)(q[8 * wd + 2 * j + 1] & 0xFF) << (8 * j);
         }
         e[wd] = ee;
         o[wd] = oo;
@@ -117,7 +132,11 @@ __device__ __forceinline__ void make_xblock(const GemvArgs& a, int m, int kb, fl
             const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __half*>(a.x) + (size_t)m * a.x_stride + 16 * (size_t)kb);
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
+#ifdef BW_TL_SKIP_LOAD
+                const uint4 q = make_uint4(0x3c003800u + kb, 0xbc00b800u, 0x40003e00u + i, 0x3555b555u);  // experiment: no global load
+#else
                 const uint4 q = __ldg(p + i);
+#endif
                 const __half2* h = reinterpret_cast<const __half2*>(&q);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -155,8 +174,12 @@ __device__ __forceinline__ void make_xblock(const GemvArgs& a, int m, int kb, fl
                 }
             }
         }
+#ifdef BW_TL_SKIP_MATH
+        e[0] = __float_as_uint(v[0]); e[1] = __float_as_uint(v[5]); o[0] = __float_as_uint(v[9]); o[1] = __float_as_uint(v[15]); s = v[3];  // experiment: no quantize
+#else
         if (a.xkind >= kXFloatI4) quantize_block<true>(v, e, o, s);
         else quantize_block<false>(v, e, o, s);
+#endif
     }
 }
 

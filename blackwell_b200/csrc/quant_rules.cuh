@@ -12,23 +12,10 @@ __device__ __forceinline__ float quant_scale_i8(float absmax) {
     float sc = absmax / 127.0f;
     return sc < 1e-10f ? 1.0f : sc;
 }
-// roundf(v / sc) with the bits of the IEEE division, at the cost of a multiplication: rcp = 1 / sc (one division per
-// block); v * rcp is within 2^-22.5 of the quotient, so the two can round to different integers only when the
-// product lies that close to a half -- those rare elements take the real division.
-__device__ __forceinline__ float div_round(float v, float sc, float rcp) {
-    const float r = v * rcp;
-    const float t = fabsf(r);
-    const float f = t - floorf(t);
-    if (fabsf(f - 0.5f) <= 1e-6f * t || !(t < 1e6f)) return roundf(v / sc);
-    return roundf(r);
-}
 __device__ __forceinline__ int quant_i8(float v, float sc) {
     float q = roundf(v / sc);
     q = fminf(127.0f, fmaxf(-127.0f, q));
     return (int)q;
-}
-__device__ __forceinline__ int quant_i8(float v, float sc, float rcp) {
-    return (int)fminf(127.0f, fmaxf(-127.0f, div_round(v, sc, rcp)));
 }
 // Reference rule for int4 activations: sc = absmax > 1e-10 ? absmax/7 : 1/7,
 // q = clamp((int)roundf(v/sc), -8, 7).
@@ -37,10 +24,6 @@ __device__ __forceinline__ float quant_scale_i4(float absmax) {
 }
 __device__ __forceinline__ int quant_i4(float v, float sc) {
     int q = (int)roundf(v / sc);
-    return max(-8, min(7, q));
-}
-__device__ __forceinline__ int quant_i4(float v, float sc, float rcp) {
-    const int q = (int)div_round(v, sc, rcp);
     return max(-8, min(7, q));
 }
 

@@ -343,7 +343,9 @@ int bw_reserve_scratch(size_t gemv_bytes, size_t attention_bytes);
  * the peer all-reduce for another rank in milliseconds (0 = default, about 2000), key 12 = 32-k columns per slab of
  * the mma.sync streaming kernel (0 = default 64), keys 13 / 14 = smallest / largest batch it takes (0 = defaults 3 and
  * 16; a smallest batch above 16 switches it off), key 15 = its ring stages (0 = automatic), key 16 = shrink the
- * small-batch kernel's ring to the tiles a CTA has (1, default) or not (0). */
+ * small-batch kernel's ring to the tiles a CTA has (1, default) or not (0), key 17 = timing experiments on the
+ * mma.sync kernel (0 = off; 1 = skip its arithmetic, 2 = skip its copies: results are then meaningless), key 18 =
+ * its packed form for up to 4 sequences on (1, default) / off (0). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);

@@ -14,9 +14,13 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def k(cuda):
+    """The kernels with the mma.sync kernel's range opened to 3..16 sequences (by default, routing by measurement
+    gives it 5..16 and leaves multi-window shapes above 8 sequences to the tcgen05 kernel)."""
     from blackwell_b200 import kernels
 
-    return kernels
+    kernels.set_tuning(13, 3)
+    yield kernels
+    kernels.set_tuning(13, 0)
 
 
 # (M, K, N): every M of the kernel's range; K = 10944 has binary16 scale rows of 1368 bytes (8 mod 16: the cp.async
@@ -144,5 +148,15 @@ def test_mma_integer_dots_equal_the_dp4a_kernel_bitwise(k):
     finally:
         k.set_tuning(13, 0)
     assert torch.equal(y16[:5], y5) and torch.equal(y5, y5d)
+    # up to 4 sequences take the packed form (both k-blocks of a column in one MMA); it can also be switched off
+    y4 = torch.empty((4, N), dtype=torch.float32, device="cuda")
+    y4u = torch.empty((4, N), dtype=torch.float32, device="cuda")
+    k.gemv_w4a8(y4, to_dev(xq[:4]), to_dev(xs[:4]), Wd, sd, K, N, 4)
+    k.set_tuning(18, 0)
+    try:
+        k.gemv_w4a8(y4u, to_dev(xq[:4]), to_dev(xs[:4]), Wd, sd, K, N, 4)
+    finally:
+        k.set_tuning(18, 1)
+    assert torch.equal(y4, y16[:4]) and torch.equal(y4u, y16[:4])
     dots = oracle.block_dots_w4a8(W, xq[3]).sum(-1) * 16
     assert np.array_equal(y16[3].cpu().numpy(), dots.astype(np.float32))
