@@ -794,6 +794,61 @@ def run_attention_only(args):
             "us_per_launch": us, "kv_bytes": nbytes, "gbs": nbytes / us / 1e3, "device_status": k.device_status()}
 
 
+def run_timeline(args):
+    """Diagnostic, needs a library built with -DBW_GEMV_TIMELINE (BW_NVCC_EXTRA=-DBW_GEMV_TIMELINE python -m
+    blackwell_b200._build -f): the small-batch GEMV kernel then stamps %globaltimer at its phase borders for its first,
+    middle and last CTA.  24 launches of one matrix (NAME[:fmt], fmt = f16 or i8 activations) rotate over 24 weight
+    copies in one CUDA graph; prints the mean phase durations of CTA 0 and the launch period."""
+    import ctypes as C
+
+    import torch
+
+    from blackwell_b200 import _lib
+    from blackwell_b200 import kernels as k
+    from blackwell_b200 import synth
+
+    L = _lib.load()
+    if not hasattr(L, "bw_debug_set_timeline"):
+        raise SystemExit("the library was built without -DBW_GEMV_TIMELINE")
+    name, _, fmt = args.timeline.partition(":")
+    fmt = fmt or "f16"
+    N, K = next((n, kk) for nm, n, kk in shapes.QWEN3_8B.gemv_set() if nm == name)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    tl = torch.zeros(16 + 32 * 48, dtype=torch.int64, device=dev)
+    L.bw_debug_set_timeline(C.c_void_p(tl.data_ptr()))
+    ncopy = 24
+    Ws = [synth.int4_weights_device(N, K, 700 + c, device=dev) for c in range(ncopy)]
+    x16 = synth.activations_f16_device(1, K, 701, device=dev)
+    xq = torch.empty((1, K), dtype=torch.int8, device=dev)
+    xs = torch.empty((1, K // 16), dtype=torch.float32, device=dev)
+    k.quantize_int8_f16(xq, xs, x16, K)
+    y = torch.empty((1, N), dtype=torch.float32, device=dev)
+    if fmt == "f16":
+        run = lambda j: k.gemv_w4a8_f16in(y, x16, Ws[j % ncopy][0], Ws[j % ncopy][1], K, N, 1)
+    else:
+        run = lambda j: k.gemv_w4a8(y, xq, xs, Ws[j % ncopy][0], Ws[j % ncopy][1], K, N, 1)
+    for j in range(3):
+        run(j)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for j in range(24):
+            run(j)
+    g.replay()
+    torch.cuda.synchronize()
+    tl.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    rec = tl.cpu().numpy()[16:].reshape(32, 3, 16)[4:24, 0, :7].astype(np.int64)
+    phases = np.diff(rec, axis=1).mean(0)
+    names = ["start->copies issued", "->dependency wait returns", "->activation prologue done", "->first tile landed",
+             "->first tile computed", "->end"]
+    return {"matrix": name, "N": N, "K": K, "activations": fmt,
+            "phase_ns": {n: round(float(v)) for n, v in zip(names, phases)},
+            "launch_period_ns": round(float(np.diff(rec[:, 0]).mean()))}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -814,6 +869,8 @@ def main():
                     "are summed across ranks (library NVLink peer-load all-reduce, or NCCL)")
     ap.add_argument("--min-time", type=float, default=MIN_TIMED_SECONDS, help="shortest timed region in seconds (each "
                     "step is timed as the mean of as many passes as that needs); 0 for profiling runs")
+    ap.add_argument("--timeline", default=None, help="diagnostic: per-phase timeline of the small-batch kernel on one "
+                    "matrix of the set, NAME[:f16|i8]; needs a library built with -DBW_GEMV_TIMELINE")
     ap.add_argument("--tune", default=None, help="profiling aid: comma list of key=value for bw_set_tuning")
     args = ap.parse_args()
     global _ONLY
@@ -831,6 +888,9 @@ def main():
         return
     if args.attn_only:
         print(json.dumps(run_attention_only(args)), flush=True)
+        return
+    if args.timeline:
+        print(json.dumps(run_timeline(args)), flush=True)
         return
     if args.decode_only:
         import torch

@@ -59,9 +59,10 @@ def _compile(src: str, verbose: bool, extra: list[str]) -> str:
 
 
 def build(verbose: bool = False, force: bool = False, extra: list[str] | None = None) -> str:
-    """Build (if stale) and return the path of the shared library."""
+    """Build (if stale) and return the path of the shared library.  Extra nvcc flags can be given in the environment
+    variable BW_NVCC_EXTRA (with -f), e.g. ``-DBW_GEMV_TIMELINE`` for the phase-timeline build of ``bench.py --timeline``."""
     os.makedirs(OBJDIR, exist_ok=True)
-    extra = extra or []
+    extra = (extra or []) + os.environ.get("BW_NVCC_EXTRA", "").split()
     srcs = _sources()
     if force:
         for f in glob.glob(os.path.join(OBJDIR, "*.o")):

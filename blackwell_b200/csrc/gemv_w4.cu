@@ -258,10 +258,10 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
     p.J = (nch + tmax - 1) / tmax;
     p.Tg = (((nch + p.J - 1) / p.J) + 31) / 32 * 32;
     const int tt = g_tune_threads.load() > 0 ? g_tune_threads.load() : 256;
+    int rg = M <= 2 ? 8 : (M <= 4 ? 4 : 2);
     p.G = tt / p.Tg;
     if (p.G < 1) p.G = 1;
     p.T = p.Tg * p.G;
-    int rg = M <= 2 ? 8 : (M <= 4 ? 4 : 2);
     if (g_tune_rg.load() > 0 && g_tune_rg.load() < rg) rg = g_tune_rg.load();
     const size_t row_nib = (size_t)K / 2, row_sc = (size_t)(K / 16) * ws_bytes;
     const size_t fixed = GemvSmem::kXOff + align128(gemv_x_smem_bytes(M, nch, p.J));

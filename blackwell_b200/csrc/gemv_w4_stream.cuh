@@ -83,29 +83,29 @@ __device__ __forceinline__ void quantize_block(const float (&v)[16], uint32_t (&
     const float sc = kInt4Rule ? quant_scale_i4(am) : quant_scale_i8(am);
     const float rcp = 1.0f / sc;
     s = sc * 0.0625f;
-    int q[16];
+    // Rounding without the conversion unit (FRND / F2I issue at a fraction of the FP32 rate, and sixteen of each per
+    // thread were most of this prologue's time): r + 1.5 * 2^23 rounds r to the nearest integer (ties to even) in the
+    // low mantissa bits, whose low byte is the two's complement result.
+    uint32_t qb[16];
     bool exact_needed = !(am < 3.0e38f);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const float r = v[i] * rcp;
-        const float ri = rintf(r);
+        const float mg = r + kMagicFloat;
+        const float ri = mg - kMagicFloat;
         exact_needed |= !(fabsf(fabsf(r - ri) - 0.5f) > 3e-5f);  // also true for a NaN
-        q[i] = (int)ri;
+        qb[i] = __float_as_uint(mg);
     }
     if (exact_needed) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) q[i] = kInt4Rule ? quant_i4(v[i], sc) : quant_i8(v[i], sc);
+        for (int i = 0; i < 16; ++i) qb[i] = (uint32_t)(kInt4Rule ? quant_i4(v[i], sc) : quant_i8(v[i], sc));
     }
+    // low bytes of four registers -> one word, even-k and odd-k elements apart
 #pragma unroll
     for (int wd = 0; wd < 2; ++wd) {
-        uint32_t ee = 0, oo = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            ee |= (uint32_t)(q[8 * wd + 2 * j] & 0xFF) << (8 * j);
-            oo |= (uint32_t)(q[8 * wd + 2 * j + 1] & 0xFF) << (8 * j);
-        }
-        e[wd] = ee;
-        o[wd] = oo;
+        const uint32_t* q = qb + 8 * wd;
+        e[wd] = prmt(prmt(q[0], q[2], 0x0040), prmt(q[4], q[6], 0x0040), 0x5410);
+        o[wd] = prmt(prmt(q[1], q[3], 0x0040), prmt(q[5], q[7], 0x0040), 0x5410);
     }
 }
 
@@ -132,11 +132,7 @@ __device__ __forceinline__ void make_xblock(const GemvArgs& a, int m, int kb, fl
             const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __half*>(a.x) + (size_t)m * a.x_stride + 16 * (size_t)kb);
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-#ifdef BW_TL_SKIP_LOAD
-                const uint4 q = make_uint4(0x3c003800u + kb, 0xbc00b800u, 0x40003e00u + i, 0x3555b555u);  // experiment: no global load
-#else
                 const uint4 q = __ldg(p + i);
-#endif
                 const __half2* h = reinterpret_cast<const __half2*>(&q);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -174,12 +170,8 @@ __device__ __forceinline__ void make_xblock(const GemvArgs& a, int m, int kb, fl
                 }
             }
         }
-#ifdef BW_TL_SKIP_MATH
-        e[0] = __float_as_uint(v[0]); e[1] = __float_as_uint(v[5]); o[0] = __float_as_uint(v[9]); o[1] = __float_as_uint(v[15]); s = v[3];  // experiment: no quantize
-#else
         if (a.xkind >= kXFloatI4) quantize_block<true>(v, e, o, s);
         else quantize_block<false>(v, e, o, s);
-#endif
     }
 }
 
