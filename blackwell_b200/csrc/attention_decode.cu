@@ -21,6 +21,7 @@
 #include "attention_mma.cuh"
 #include "common.cuh"
 #include "host_util.h"
+#include "rope_norm.cuh"
 
 namespace bw {
 
@@ -50,6 +51,12 @@ struct AttnArgs {
     float scale;
     float* part;           // [M][nqh][nsplit][130] when nsplit > 1
     unsigned int* tickets; // [M][nkv] arrival counters (zero between calls): the last split CTA merges; or nullptr
+    // fused form (tensor-core kernel only): Q, and the K / V rows of the new position, come straight from the QKV
+    // projection output [M][(nqh + 2 nkv) * 128]; qkv == nullptr selects the plain form
+    const float* qkv;
+    const float* q_norm_w;
+    const float* k_norm_w;
+    float eps, rope_base;
 };
 
 // Partial record of one (sequence, head, split): 128 un-normalised outputs, then max and sum.
@@ -251,7 +258,31 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const 
     __shared__ int s_last;
     // The per-warp results reuse the warp's own K/V staging area once its stream has drained.
     auto s_o = [&](int w, int h) { return reinterpret_cast<float*>(attn_dsm + w * amma::kWarpSmem) + h * kHd; };
-    for (int i = t; i < GQ * kHd; i += blockDim.x) s_q[i / kHd][i % kHd] = a.Q[((size_t)m * a.nqh + h0) * kHd + i];
+    if (a.qkv == nullptr) {
+        for (int i = t; i < GQ * kHd; i += blockDim.x) s_q[i / kHd][i % kHd] = a.Q[((size_t)m * a.nqh + h0) * kHd + i];
+    } else {
+        // Fused head norm + RoPE + cache write (what bw_qk_norm_rope_kv_f16 does in a launch of its own): every CTA
+        // norms and rotates its own query heads; the CTA whose split holds the new position also norms and rotates that
+        // position's K row, converts its V row, stores both in the cache and then streams them like any other row.
+        const int heads = a.nqh + 2 * a.nkv;
+        const float* row = a.qkv + (size_t)m * heads * kHd;
+        for (int h = warp; h < GQ; h += kAttnWarps) {
+            float4 v = *reinterpret_cast<const float4*>(row + (size_t)(h0 + h) * kHd + 4 * lane);
+            v = head_norm_rope(v, a.q_norm_w, a.eps, seq_pos, a.rope_base, lane);
+            *reinterpret_cast<float4*>(&s_q[h][4 * lane]) = v;
+        }
+        if (seq_pos >= p0 && seq_pos < p1 && seq_pos < a.max_seq && warp < 2) {
+            __half* Kw = const_cast<__half*>(Kb) + (size_t)seq_pos * kHd + 4 * lane;
+            __half* Vw = const_cast<__half*>(Vb) + (size_t)seq_pos * kHd + 4 * lane;
+            if (warp == 0) {
+                float4 v = *reinterpret_cast<const float4*>(row + (size_t)(a.nqh + kvh) * kHd + 4 * lane);
+                store_half4(Kw, head_norm_rope(v, a.k_norm_w, a.eps, seq_pos, a.rope_base, lane));
+            } else {
+                store_half4(Vw, *reinterpret_cast<const float4*>(row + (size_t)(a.nqh + a.nkv + kvh) * kHd + 4 * lane));
+            }
+            __threadfence();  // the rows are read back through cp.async (L2) by all four warps
+        }
+    }
     __syncthreads();
 
     float m_run, l_run, o[32];
@@ -358,23 +389,29 @@ static int choose_splits(int pairs, int ctx, int slots) {
     return best;
 }
 
+// The arrival counters live in a region of fixed size at the front of the scratch block that nothing else ever
+// uses: they must read zero at the start of every call (the last arriver leaves them so), and a region whose size
+// followed the problem would let one call's partial records lie where a later, larger call expects its counters.
+constexpr size_t kTicketBytes = 65536;   // 16,384 (sequence, kv head) pairs; beyond that the context is not split
+
 // Upper bound of the scratch a call with up to M sequences and a context hint up to ctx can need.
 size_t attn_scratch_bytes(int M, int nqh, int nkv, int ctx) {
     if (M < 1 || nqh < 1 || nkv < 1 || ctx < 1) return 0;
-    const size_t tick_bytes = (((size_t)M * nkv * sizeof(unsigned int)) + 255) & ~(size_t)255;
-    return tick_bytes + (size_t)M * nqh * 64 * kPartStride * sizeof(float);  // at most 64 splits
+    return kTicketBytes + (size_t)M * nqh * 64 * kPartStride * sizeof(float);  // at most 64 splits
 }
 
 template <typename KVT>
 static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
-    if (!a.out || !a.Q || !a.K || !a.V || a.nqh < 1 || a.nkv < 1 || a.nqh % a.nkv != 0 || a.M < 1 || a.max_seq < 1)
+    if (!a.out || (!a.Q && !a.qkv) || !a.K || !a.V || a.nqh < 1 || a.nkv < 1 || a.nqh % a.nkv != 0 || a.M < 1 || a.max_seq < 1)
         return cudaErrorInvalidValue;
     const int gq = a.nqh / a.nkv;
     if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return cudaErrorInvalidValue;
     if (ctx_hint < 1) ctx_hint = 1;
     if (ctx_hint > a.max_seq) ctx_hint = a.max_seq;
-    const bool use_mma = sizeof(KVT) == 2 && (gq == 4 || gq == 8) && g_attn_mma;  // binary16 cache with grouped heads
+    const bool use_mma = sizeof(KVT) == 2 && (gq == 4 || gq == 8) && (g_attn_mma || a.qkv);  // binary16 cache with grouped heads
+    if (a.qkv && !use_mma) return cudaErrorInvalidValue;  // the fused form exists in the tensor-core kernel only
     int nsplit = choose_splits(a.M * a.nkv, ctx_hint, 2 * sm_count(current_device()));
+    if ((size_t)a.M * a.nkv * sizeof(unsigned int) > kTicketBytes) nsplit = 1;  // thousands of pairs fill the GPU unsplit
     a.split_len = (ctx_hint + nsplit - 1) / nsplit;
     a.split_len = (a.split_len + kPosPerStep - 1) / kPosPerStep * kPosPerStep;
     nsplit = (ctx_hint + a.split_len - 1) / a.split_len;
@@ -384,7 +421,7 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     a.tickets = nullptr;
     if (nsplit > 1) {
         // scratch = [arrival counters, one per (sequence, kv head)] [partial records]
-        const size_t tick_bytes = (((size_t)a.M * a.nkv * sizeof(unsigned int)) + 255) & ~(size_t)255;
+        const size_t tick_bytes = kTicketBytes;
         unsigned char* base = nullptr;
         cudaError_t e = g_attn_scratch.get(tick_bytes + (size_t)a.M * a.nqh * nsplit * kPartStride * sizeof(float),
                                            (size_t)4 << 20, st, &base);
@@ -453,6 +490,20 @@ extern "C" int bw_attention_decode_f16kv(float* output, const float* Q, const ui
     a.out = output; a.Q = Q; a.K = K_cache; a.V = V_cache; a.d_seq_pos = d_seq_pos; a.per_seq = 1;
     a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
     a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
+    return attn_launch<__half>(a, ctx_hint > 0 ? ctx_hint : max_seq_len, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_attention_decode_f16kv_fused(float* output, const float* qkv, const float* q_norm_w,
+                                               const float* k_norm_w, uint16_t* K_cache, uint16_t* V_cache,
+                                               const int* d_seq_pos, int ctx_hint, int num_q_heads, int num_kv_heads,
+                                               int head_dim, int max_seq_len, int M, size_t kv_batch_elems,
+                                               size_t kv_layer_elems, float eps, float rope_base, void* stream) {
+    if (head_dim != kHd || !d_seq_pos || !qkv || !q_norm_w || !k_norm_w) return cudaErrorInvalidValue;
+    AttnArgs a{};
+    a.out = output; a.Q = nullptr; a.K = K_cache; a.V = V_cache; a.d_seq_pos = d_seq_pos; a.per_seq = 1;
+    a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
+    a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
+    a.qkv = qkv; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.eps = eps; a.rope_base = rope_base;
     return attn_launch<__half>(a, ctx_hint > 0 ? ctx_hint : max_seq_len, static_cast<cudaStream_t>(stream));
 }
 

@@ -4,7 +4,7 @@
 // quantize -> q/k/v GEMV -> head norm, RoPE -> KV update -> attention -> quantize -> o GEMV -> residual -> rmsnorm ->
 // quantize -> gate/up GEMV -> SwiGLU -> quantize -> down GEMV -> residual; then final norm, LM head, sampling) and the
 // graph form of bench/decode_int4_cgraph_8b.cu:249-399 (stream capture, instantiate, launch per step), with the
-// fusions of this library: 7 launches per layer for the whole batch, per-sequence positions and token bookkeeping in
+// fusions of this library: 6 or 7 launches per layer for the whole batch, per-sequence positions and token bookkeeping in
 // device memory, and ONE CUDA graph per step that is captured at creation and only replayed afterwards -- no
 // allocation, no host-device synchronisation and no host decision inside a generation.
 //
@@ -199,10 +199,15 @@ int enqueue_step(bw_decode* d, cudaStream_t st) {
         const Layer& L = d->layers[l];
         const size_t off = (size_t)l * d->kv_layer;
         BW_TRY(gemv(d, L.qkv, d->qkv, nullptr, d->x, nullptr, 0, L.rn_in, L.qkv.N, st));
-        BW_TRY(bw_qk_norm_rope_kv_f16(d->q, d->kc, d->vc, d->qkv, L.qn, L.kn, d->pos, nq, nkv, 128, c.max_seq, M, d->kv_batch,
-                                      off, c.eps, c.rope_base, st));
-        BW_TRY(bw_attention_decode_f16kv(d->attn, d->q, d->kc, d->vc, d->pos, c.max_seq, nq, nkv, 128, c.max_seq, M,
-                                         d->kv_batch, off, st));
+        if (nq / nkv == 4 || nq / nkv == 8) {  // head norm + RoPE + KV write inside the tensor-core attention kernel
+            BW_TRY(bw_attention_decode_f16kv_fused(d->attn, d->qkv, L.qn, L.kn, d->kc, d->vc, d->pos, c.max_seq, nq, nkv, 128,
+                                                   c.max_seq, M, d->kv_batch, off, c.eps, c.rope_base, st));
+        } else {
+            BW_TRY(bw_qk_norm_rope_kv_f16(d->q, d->kc, d->vc, d->qkv, L.qn, L.kn, d->pos, nq, nkv, 128, c.max_seq, M,
+                                          d->kv_batch, off, c.eps, c.rope_base, st));
+            BW_TRY(bw_attention_decode_f16kv(d->attn, d->q, d->kc, d->vc, d->pos, c.max_seq, nq, nkv, 128, c.max_seq, M,
+                                             d->kv_batch, off, st));
+        }
         BW_TRY(gemv(d, L.o, d->x, d->x, d->attn, nullptr, 0, nullptr, H, st));
         BW_TRY(gemv(d, L.gu, d->gu, nullptr, d->x, nullptr, 0, L.rn_post, 2 * I, st));
         BW_TRY(gemv(d, L.down, d->x, d->x, d->gu, d->gu + I, 2 * (long)I, nullptr, H, st));

@@ -8,6 +8,7 @@
 #include "../../include/blackwell_b200.h"
 #include "common.cuh"
 #include "host_util.h"
+#include "rope_norm.cuh"
 
 namespace bw {
 
@@ -33,19 +34,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_kernel(float* q_out, __ha
     const int pos = d_seq_pos[m];
     float4 v = *reinterpret_cast<const float4*>(qkv + ((size_t)m * heads + h) * kHeadDim + 4 * lane);
     const bool is_q = h < nqh, is_k = !is_q && h < nqh + nkv;
-    if (is_q || is_k) {
-        float ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        ss = warp_sum(ss);
-        const float is = rsqrtf(ss / (float)kHeadDim + eps);
-        const float4 w = *reinterpret_cast<const float4*>((is_q ? q_norm_w : k_norm_w) + 4 * lane);
-        v.x = v.x * is * w.x; v.y = v.y * is * w.y; v.z = v.z * is * w.z; v.w = v.w * is * w.w;
-        const float t0 = (float)pos * powf(rope_base, -2.0f * (float)(2 * lane) / (float)kHeadDim);
-        const float t1 = (float)pos * powf(rope_base, -2.0f * (float)(2 * lane + 1) / (float)kHeadDim);
-        const float c0 = cosf(t0), s0 = sinf(t0), c1 = cosf(t1), s1 = sinf(t1);
-        const float4 r = make_float4(v.x * c0 - v.y * s0, v.x * s0 + v.y * c0, v.z * c1 - v.w * s1,
-                                     v.z * s1 + v.w * c1);
-        v = r;
-    }
+    if (is_q || is_k) v = head_norm_rope(v, is_q ? q_norm_w : k_norm_w, eps, pos, rope_base, lane);
     if (is_q) {
         *reinterpret_cast<float4*>(q_out + ((size_t)m * nqh + h) * kHeadDim + 4 * lane) = v;
     } else {
@@ -54,11 +43,7 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kv_kernel(float* q_out, __ha
         const int kvh = is_k ? h - nqh : h - nqh - nkv;
         __half* dst = (is_k ? k_cache : v_cache) + (size_t)m * kv_batch_elems + kv_layer_elems +
                       ((size_t)kvh * max_seq + pos) * kHeadDim + 4 * lane;
-        const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
-        uint2 u;
-        u.x = *reinterpret_cast<const uint32_t*>(&a);
-        u.y = *reinterpret_cast<const uint32_t*>(&b);
-        *reinterpret_cast<uint2*>(dst) = u;
+        store_half4(dst, v);
     }
 }
 

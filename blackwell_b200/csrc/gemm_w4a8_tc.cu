@@ -514,6 +514,8 @@ static cudaError_t launch_n(const CUtensorMap& map_w, const TcArgs& t, int grid,
 }
 
 // Launch geometry and scratch layout of one call: [tickets][activation chunks][K-split partials].
+constexpr size_t kTicketBytes = 65536;  // 16,384 row tiles; larger matrices are not K-split
+
 struct TcLayout {
     int Mpad, nchunks, tiles, ksplit;
     size_t xb_off, part_off, part_bytes;
@@ -530,8 +532,11 @@ static TcLayout tc_layout(int M, int N, int K) {
     l.ksplit = ksplit;
     const size_t xb_bytes = (size_t)l.nchunks * xb_chunk_bytes(l.Mpad);
     l.part_bytes = ksplit > 1 ? (size_t)l.tiles * ksplit * l.Mpad * kRows * sizeof(float) : 0;
-    const size_t ticket_bytes = (size_t)l.tiles * sizeof(unsigned int);
-    l.xb_off = (ticket_bytes + 255) & ~(size_t)255;
+    // The arrival counters own a region of fixed size at the front of the block: they must read zero at the start of
+    // every call, and a region sized by the problem would let one call's activations lie where a later, larger call
+    // expects its counters.
+    if ((size_t)l.tiles * sizeof(unsigned int) > kTicketBytes) { l.ksplit = 1; l.part_bytes = 0; }
+    l.xb_off = kTicketBytes;
     l.part_off = (l.xb_off + xb_bytes + 255) & ~(size_t)255;
     return l;
 }

@@ -4,8 +4,8 @@ The call sequence is the reference's per-layer loop
 (server/inference_server_int4_batched.cu:253-298) with the fusions applied: per layer
 
     qkv  = W_qkv  . q8(rmsnorm(x, rn_in))                      bw_gemv_w4a8_decode (norm prologue)
-    q, K[pos], V[pos] = head-norm + RoPE + cache write          bw_qk_norm_rope_kv_f16
-    attn = GQA attention over the binary16 cache                bw_attention_decode_f16kv
+    q, K[pos], V[pos] = head-norm + RoPE + cache write          bw_qk_norm_rope_kv_f16        } one launch with 4 or 8 query
+    attn = GQA attention over the binary16 cache                bw_attention_decode_f16kv     } heads per kv head (_fused)
     x    = x + W_o . q8(attn)                                   bw_gemv_w4a8_decode (residual epilogue)
     gu   = W_gu . q8(rmsnorm(x, rn_post))                       bw_gemv_w4a8_decode (norm prologue)
     x    = x + W_down . q8(silu(gate) * up)                     bw_gemv_w4a8_decode (SwiGLU prologue + residual)
@@ -199,10 +199,15 @@ class DecodeEngine:
             off = l * self.kv_layer
             k.gemv_w4a8_decode(self.qkv, 0, None, self.x, None, 0, L["rn_in"], eps, L["qkv"][0], L["qkv"][1], H,
                                self.qkv_n, M)
-            k.qk_norm_rope_kv_f16(self.q, self.kc, self.vc, self.qkv, L["qn"], L["kn"], self.pos, self.nq, self.nkv,
-                                  128, self.max_seq, M, self.kv_batch, off, eps, ROPE_BASE)
-            k.attention_decode_f16kv(self.attn, self.q, self.kc, self.vc, self.pos, self.ctx_hint, self.nq, self.nkv,
-                                     128, self.max_seq, M, self.kv_batch, off)
+            if self.nq // self.nkv in (4, 8):   # head norm + RoPE + KV write inside the tensor-core attention kernel
+                k.attention_decode_f16kv_fused(self.attn, self.qkv, L["qn"], L["kn"], self.kc, self.vc, self.pos,
+                                               self.ctx_hint, self.nq, self.nkv, 128, self.max_seq, M, self.kv_batch,
+                                               off, eps, ROPE_BASE)
+            else:
+                k.qk_norm_rope_kv_f16(self.q, self.kc, self.vc, self.qkv, L["qn"], L["kn"], self.pos, self.nq,
+                                      self.nkv, 128, self.max_seq, M, self.kv_batch, off, eps, ROPE_BASE)
+                k.attention_decode_f16kv(self.attn, self.q, self.kc, self.vc, self.pos, self.ctx_hint, self.nq,
+                                         self.nkv, 128, self.max_seq, M, self.kv_batch, off)
             if self.world == 1:
                 k.gemv_w4a8_decode(self.x, 0, self.x, self.attn, None, 0, None, 0.0, L["o"][0], L["o"][1],
                                    self.nq * 128, H, M)

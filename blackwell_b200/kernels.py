@@ -248,3 +248,12 @@ def sample_argmax_candidates(logits, row_stride, vocab, M, index_offset, cand_ou
 def sample_argmax_merge(cand_all_pairs, world, M, out_ids, seq_pos_to_advance=None, pos_limit=0, stream=None):
     _chk("sample_argmax_merge", _L.bw_sample_argmax_merge(_p(cand_all_pairs), world, M, _p(out_ids),
                                                           _p(seq_pos_to_advance), int(pos_limit), _s(stream)))
+
+
+def attention_decode_f16kv_fused(output, qkv, q_norm_w, k_norm_w, k_cache, v_cache, d_seq_pos, ctx_hint, num_q_heads,
+                                 num_kv_heads, head_dim, max_seq_len, M, kv_batch_elems, kv_layer_elems, eps, rope_base,
+                                 stream=None):
+    _chk("attention_decode_f16kv_fused", _L.bw_attention_decode_f16kv_fused(
+        _p(output), _p(qkv), _p(q_norm_w), _p(k_norm_w), _p(k_cache), _p(v_cache), _p(d_seq_pos), ctx_hint,
+        num_q_heads, num_kv_heads, head_dim, max_seq_len, M, C.c_size_t(kv_batch_elems), C.c_size_t(kv_layer_elems),
+        C.c_float(eps), C.c_float(rope_base), _s(stream)))

@@ -203,6 +203,19 @@ int bw_sample_argmax_candidates(const float* logits, long row_stride, int vocab,
 int bw_sample_argmax_merge(const int* cand_all_pairs, int world, int M, int* out_ids,
                            int* seq_pos_to_advance_or_null, int pos_limit, void* stream);
 
+/* bw_qk_norm_rope_kv_f16 + bw_attention_decode_f16kv in ONE launch: qkv f32 [M][(nqh + 2 nkv) * 128] is the output
+ * of the fused QKV projection; every CTA norms and rotates its own query heads, and the CTA whose context split
+ * holds the sequence's position norms, rotates and stores that position's K row and stores its V row before
+ * streaming the cache (a position outside the cache is not written).  Only for the shapes the tensor-core kernel
+ * takes -- binary16 cache, 4 or 8 query heads per kv head -- otherwise cudaErrorInvalidValue.  Replaces, with the
+ * attention call, head_norm_kernel / apply_rope_kernel / update_kv_cache of
+ * server/inference_server_int4_batched.cu:49-70,262-266. */
+int bw_attention_decode_f16kv_fused(float* output, const float* qkv, const float* q_norm_w, const float* k_norm_w,
+                                    uint16_t* K_cache, uint16_t* V_cache, const int* d_seq_pos, int ctx_hint,
+                                    int num_q_heads, int num_kv_heads, int head_dim, int max_seq_len, int M,
+                                    size_t kv_batch_elems, size_t kv_layer_elems, float eps, float rope_base,
+                                    void* stream);
+
 /* Attention for callers that must not allocate.  No counterpart in the reference: it exists for hosts
  * that cannot reach the CUDA allocator once they are serving -- a process that has given all device memory
  * to its own pool, or one that runs with allocation switched off or audited after start-up.  Arguments,

@@ -34,18 +34,20 @@ def cpu_gemv(x, W, sc16):
     return oracle.gemv_w4a8_f64(q, s, W, sc16).astype(np.float32)
 
 
-def test_decode_step_matches_cpu_chain(cuda):
+@pytest.mark.parametrize("M", [3, 16])
+def test_decode_step_matches_cpu_chain(cuda, M):
+    """Batch 3 runs the dp4a GEMV kernel, batch 16 the mma.sync one."""
     import torch
 
     from blackwell_b200.decode import ROPE_BASE, DecodeEngine
 
-    s, M, max_seq, ctx = SMALL, 3, 96, 40
+    s, max_seq, ctx = SMALL, 96, 40
     hw = HostWeights()
     eng = DecodeEngine(s, M, max_seq, cuda, seed=5, host_weights=hw)
     eng.fill_cache(ctx)
-    pos0 = np.array([ctx - 1, ctx - 5, 3], np.int32)
+    pos0 = np.array([ctx - 1, ctx - 5, 3] + [(5 * i) % ctx for i in range(M - 3)], np.int32)
     eng.pos.copy_(torch.from_numpy(pos0))
-    toks = np.array([7, 1002, 500], np.int32)
+    toks = np.array([7, 1002, 500] + [(91 * i + 13) % s.vocab for i in range(M - 3)], np.int32)
     eng.set_tokens(toks)
     Kc = eng.kc.cpu().numpy().copy()
     Vc = eng.vc.cpu().numpy().copy()
@@ -76,10 +78,13 @@ def test_decode_step_matches_cpu_chain(cuda):
         x = x + cpu_gemv(act, *hw.np[sd + 4])
     logits = cpu_gemv(oracle.rmsnorm(x, eng.rn_final.cpu().numpy()), *hw.np[5 + 900001])
 
-    assert max_abs_rel(eng.x.cpu().numpy(), x) < 2e-3
-    assert max_abs_rel(eng.logits.cpu().numpy(), logits) < 2e-3
+    # a rounding tie of the int8 activation quantizer resolved the other way (rsqrtf, summation order) moves one
+    # element by a whole step; with 16 sequences such flips are five times as likely as with 3
+    tol = 2e-3 if M <= 3 else 5e-3
+    assert max_abs_rel(eng.x.cpu().numpy(), x) < tol
+    assert max_abs_rel(eng.logits.cpu().numpy(), logits) < tol
     got_k = eng.kc.cpu().numpy().reshape(M, s.layers, nkv, max_seq, 128).astype(np.float32)
-    assert max_abs_rel(got_k, Kc.astype(np.float32)) < 2e-3
+    assert max_abs_rel(got_k, Kc.astype(np.float32)) < tol
     # greedy ids: equal wherever the CPU's top-2 margin exceeds the numerical noise
     ids = eng.tokens.cpu().numpy()
     for m in range(M):
@@ -160,6 +165,40 @@ def test_qk_norm_rope_kv_and_embed_and_batched_argmax(cuda):
         k.sample_argmax_batched(to_dev(logits), Vv, Vv, M, ids, p)
     assert [int(i) for i in ids.cpu()] == [oracle.argmax(logits[m]) for m in range(M)]
     assert np.array_equal(p.cpu().numpy(), pos + 2)
+
+
+@pytest.mark.parametrize("nq,nkv", [(8, 2), (8, 1), (32, 8)])
+def test_fused_norm_rope_kv_attention_equals_the_two_launches(cuda, nq, nkv):
+    """bw_attention_decode_f16kv_fused against bw_qk_norm_rope_kv_f16 + bw_attention_decode_f16kv on the same inputs:
+    same arithmetic, so the attention output and the cache rows must be bit-identical; positions at 0, inside and at
+    the end of a split, beyond the context hint, and one outside the cache (not written)."""
+    import torch
+
+    from blackwell_b200 import kernels as k
+
+    M, max_seq, hint = 6, 700, 300
+    g = synth.rng(440 + nq + nkv)
+    qkv = to_dev(g.normal(size=(M, (nq + 2 * nkv) * 128)).astype(np.float32))
+    qn, kn = to_dev(synth.norm_weight(128, 441)), to_dev(synth.norm_weight(128, 442))
+    pos = to_dev(np.array([0, 63, 64, 299, 650, 700], np.int32))
+    layers, layer = 2, 1
+    kv_layer = nkv * max_seq * 128
+    base = synth.kv_cache_f16((M, layers * kv_layer), 443)
+    kc1 = to_dev(base.view(np.uint16)).view(torch.float16)
+    vc1 = to_dev(synth.kv_cache_f16((M, layers * kv_layer), 444).view(np.uint16)).view(torch.float16)
+    kc2, vc2 = kc1.clone(), vc1.clone()
+    q = torch.empty((M, nq * 128), dtype=torch.float32, device="cuda")
+    out1 = torch.empty((M, nq * 128), dtype=torch.float32, device="cuda")
+    out2 = torch.full_like(out1, float("nan"))
+    k.qk_norm_rope_kv_f16(q, kc1, vc1, qkv, qn, kn, pos, nq, nkv, 128, max_seq, M, layers * kv_layer, layer * kv_layer,
+                          1e-6, 1e6)
+    k.attention_decode_f16kv(out1, q, kc1, vc1, pos, hint, nq, nkv, 128, max_seq, M, layers * kv_layer, layer * kv_layer)
+    k.attention_decode_f16kv_fused(out2, qkv, qn, kn, kc2, vc2, pos, hint, nq, nkv, 128, max_seq, M, layers * kv_layer,
+                                   layer * kv_layer, 1e-6, 1e6)
+    torch.cuda.synchronize()
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert torch.equal(out1, out2)
+    assert k.device_status() == 0
 
 
 def test_tensor_parallel_argmax_candidates_and_merge(cuda):

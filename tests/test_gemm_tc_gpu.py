@@ -12,9 +12,13 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def k(cuda):
+    """The kernels with the mma.sync kernel switched off, so that every batch from 8 sequences up takes the tcgen05
+    kernel as it does by default above 16."""
     from blackwell_b200 import kernels
 
-    return kernels
+    kernels.set_tuning(13, 99)
+    yield kernels
+    kernels.set_tuning(13, 0)
 
 
 CASES = [(16, 256, 128), (9, 4096, 128), (16, 4096, 300), (17, 512, 129), (32, 4096, 1024), (33, 2048, 640),
@@ -102,3 +106,20 @@ def test_tc_matches_small_batch_kernel_bitwise_dots(k):
     assert torch.equal(y16[:7], y7)
     dots = oracle.block_dots_w4a8(W, xq[3]).sum(-1) * 16
     assert np.array_equal(y16[3].cpu().numpy(), dots.astype(np.float32))
+
+
+def test_tc_arrival_counters_survive_a_smaller_call_before_a_larger_one(k):
+    """K-split row tiles count arrivals in the scratch block; a matrix with few tiles followed by one with many once
+    found the earlier call's prepared activations where it expected zeroed counters (they now own a fixed region)."""
+    import torch
+
+    M, K = 32, 2048
+    for N, seed in [(256, 950), (9000, 951), (384, 952), (12800, 953)]:
+        W, sc16, _ = synth.int4_weights(N, K, seed=seed)
+        x16 = synth.activations_f16(M, K, seed + 30)
+        xq, xs = oracle.quantize_int8(x16.astype(np.float32))
+        y = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        k.gemv_w4a8_f16in(y, to_dev(x16.view(np.uint16)), to_dev(W), to_dev(sc16.view(np.uint16)), K, N, M)
+        torch.cuda.synchronize()
+        assert k.device_status() == 0
+        assert max_abs_rel(y.cpu().numpy(), oracle.gemv_w4a8_f64(xq, xs, W, sc16)) < 2e-5, N

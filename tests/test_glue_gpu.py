@@ -241,6 +241,26 @@ def test_attention_matches_reference_cuda_short_context(k):
     print("reference attention vs oracle:", max_abs_rel(b.cpu().numpy(), ref))
 
 
+def test_attention_arrival_counters_survive_a_smaller_call_before_a_larger_one(k):
+    """The split kernels count arrivals in the library's scratch block.  A call with few (sequence, kv head) pairs
+    followed by one with many once found the earlier call's partial records where it expected zeroed counters; the
+    counters now own a fixed region."""
+    import torch
+
+    hd, max_seq = 128, 640
+    for M, nqh, nkv, seed in [(2, 32, 8, 240), (24, 32, 8, 241), (3, 16, 4, 242), (40, 8, 8, 243)]:
+        g = synth.rng(seed)
+        Q = g.normal(size=(M, nqh * hd)).astype(np.float32)
+        Kc = synth.kv_cache_f16((M, nkv, max_seq, hd), seed + 10)
+        Vc = synth.kv_cache_f16((M, nkv, max_seq, hd), seed + 20)
+        pos = np.array([max_seq - 1 - 11 * (m % 9) for m in range(M)], np.int32)
+        out = torch.full((M, nqh * hd), float("nan"), dtype=torch.float32, device="cuda")
+        k.attention_decode_f16kv(out, to_dev(Q), to_dev(Kc.view(np.uint16)), to_dev(Vc.view(np.uint16)), to_dev(pos),
+                                 max_seq, nqh, nkv, hd, max_seq, M, nkv * max_seq * hd, 0)
+        ref = oracle.attention_decode_f16kv(Q, Kc, Vc, pos, nqh, nkv, hd, max_seq, M)
+        assert max_abs_rel(out.cpu().numpy(), ref) < 1e-4, (M, nqh, nkv)
+
+
 @pytest.mark.parametrize("nqh,nkv", [(32, 8), (4, 2)])
 def test_attention_f16_cache_context_longer_than_the_hint(k, nqh, nkv):
     """The context hint only sizes the splits: sequences that have grown well past it (a captured step replayed many
