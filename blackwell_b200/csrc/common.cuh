@@ -40,6 +40,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same probe with a suspend-time hint: the hardware may keep the thread parked for up to `ns` nanoseconds while the
+// phase is incomplete (it wakes when the phase completes), so a waiting warp issues few instructions.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -59,6 +72,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (clock64() - t0 > 2500000000ll) return false;  // more than a second at any SM clock
+    }
+}
+
+// The same bounded wait for roles that wait long and share their scheduler with working warps: parked probes.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait_parked(bar, parity, 4000u)) return true;
+        if (clock64() - t0 > 2500000000ll) return false;
     }
 }
 

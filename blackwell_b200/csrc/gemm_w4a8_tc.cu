@@ -12,14 +12,19 @@
 #include "host_util.h"
 
 namespace bw {
+#ifdef BW_GEMV_TIMELINE
+void* debug_timeline_ptr();
+#define TC_TL(slot, idx) do { if (blockIdx.x == 0 && a.timeline && (idx) < 256) a.timeline[(slot) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define TC_TL(slot, idx) do { } while (0)
+#endif
 namespace tc {
 
 // ----------------------------------------------------------------------------------------------------------
 // Activation prep: quantizes every 16-element k-block of every sequence once (the same make_xblock code as the
 // streaming kernel's prologue: plain / RMSNorm / SwiGLU, int8 rule) and stores it in the layout the MMA's B
 // operand wants, chunk by chunk:
-//   chunk c: 8 block pairs, each [even block: Mpad rows x 16 B][Mpad rows of zeros][odd block]   then
-//            [block 0..15][Mpad] float scales / 16
+//   chunk c: [block 0..15][Mpad rows x 16 B]   then   [block 0..15][Mpad] float scales / 16 * 2^39
 // Rows >= M and k-blocks >= K/16 are zero with scale 0.  Grid (ceil(nkb_pad / 256), Mpad), 256 threads.
 // ----------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) prep_x_kernel(unsigned char* xb, const GemvArgs a, int M, int Mpad,
@@ -55,11 +60,8 @@ __global__ void __launch_bounds__(256) prep_x_kernel(unsigned char* xb, const Ge
     if (m < M && kb < nkb) make_xblock(a, m, kb, rstd, e, o, s);
     const int c = kb / kBlocksPerChunk, b = kb % kBlocksPerChunk;
     unsigned char* chunk = xb + (size_t)c * xb_chunk_bytes(Mpad);
-    // pair layout [even block][zeros][odd block], Mpad rows of 16 bytes each; the even block's thread writes the zeros
-    const size_t slot = (size_t)(b >> 1) * 3 + (size_t)(b & 1) * 2;
-    *reinterpret_cast<uint4*>(chunk + (slot * Mpad + m) * 16) = make_uint4(e[0], o[0], e[1], o[1]);
-    if ((b & 1) == 0) *reinterpret_cast<uint4*>(chunk + ((slot + 1) * Mpad + m) * 16) = make_uint4(0u, 0u, 0u, 0u);
-    reinterpret_cast<float*>(chunk + (size_t)b_chunk_bytes(Mpad))[b * Mpad + m] = s;
+    *reinterpret_cast<uint4*>(chunk + ((size_t)b * Mpad + m) * 16) = make_uint4(e[0], o[0], e[1], o[1]);
+    reinterpret_cast<float*>(chunk + (size_t)b_chunk_bytes(Mpad))[b * Mpad + m] = s * kXScaleUp;
 }
 
 // ----------------------------------------------------------------------------------------------------------
@@ -72,7 +74,7 @@ __host__ __device__ constexpr int sub_chunks(int Mpad) { return Mpad > 0 ? 2 : 2
 __host__ __device__ constexpr int packed_slots(int Mpad) { return Mpad <= 16 ? 3 : 2; }
 // The activation ring runs deeper than the operand ring: its slots are refilled from L2 only after the MMAs that
 // read them retire, and with two slots that latency was the period of the whole pipeline.
-__host__ __device__ constexpr int b_slots(int Mpad) { return Mpad <= 32 ? 4 : 2; }
+__host__ __device__ constexpr int b_slots(int Mpad) { return Mpad <= 32 ? 4 : 3; }
 __host__ __device__ constexpr int s_slots(int Mpad) { return Mpad <= 32 ? 4 : 3; }
 __host__ __device__ constexpr int packed_slot_bytes(int Mpad) { return kRows * 128 * sub_chunks(Mpad); }
 
@@ -87,8 +89,14 @@ struct Smem {
     __host__ __device__ static constexpr int scales(int Mpad) { return b_off(Mpad) + b_slots(Mpad) * b_chunk_bytes(Mpad); }
     __host__ __device__ static constexpr int scale_slot_bytes(int Mpad) { return kBlocksPerChunk * Mpad * 4; }  // x_sc / 16
     __host__ __device__ static constexpr int wscales(int Mpad) { return scales(Mpad) + s_slots(Mpad) * scale_slot_bytes(Mpad); }
-    __host__ __device__ static constexpr int total(int Mpad) { return wscales(Mpad) + kSW * kWScaleBytes; }  // weight-scale ring
+    __host__ __device__ static constexpr int const_a(int Mpad) { return wscales(Mpad) + kSW * kWScaleBytes; }  // 128 rows x 16 B of -128
+    __host__ __device__ static constexpr int const_b(int Mpad) { return const_a(Mpad) + kRows * 16; }           // Mpad rows x 16 B of -127
+    __host__ __device__ static constexpr int total(int Mpad) { return const_b(Mpad) + Mpad * 16; }
 };
+// The 512 accumulator columns form a ring of four groups: the MMAs of a group are issued as soon as every epilogue
+// warp has read the group four back, so a slow warp delays the tensor core only after three groups of slack (with
+// two groups the epilogue waited about 400 cycles for the next group's MMAs at every group boundary).
+constexpr int kGroups = 2, kGroupCols = 512 / kGroups;
 // barrier indices
 enum : int {
     kFullP = 0,                 // + slot (up to 4): packed nibbles landed
@@ -99,9 +107,9 @@ enum : int {
     kFreeB = kFullB + 4,        // MMAs that read the activation slot have completed
     kFullS = kFreeB + 4,        // + slot (up to 4): scales landed
     kEmptyS = kFullS + 4,       // scales consumed by the epilogue
-    kDFull = kEmptyS + 4,       // + group (2): accumulator group complete
-    kDEmpty = kDFull + 2,       // accumulator group read out
-    kFullW = kDEmpty + 2,       // + slot (kSW): weight scales of a chunk landed
+    kDFull = kEmptyS + 4,       // + group (kGroups): accumulator group complete
+    kDEmpty = kDFull + kGroups, // accumulator group read out
+    kFullW = kDEmpty + kGroups,       // + slot (kSW): weight scales of a chunk landed
     kEmptyW = kFullW + kSW,     // weight scales consumed
     kNumBars = kEmptyW + kSW,
 };
@@ -109,7 +117,7 @@ enum : int {
 template <int NMMA>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
-    constexpr int GB = 256 / NMMA;                      // k-blocks per accumulator group (256 TMEM columns)
+    constexpr int GB = kGroupCols / NMMA;               // k-blocks per accumulator group
     constexpr int GPC = kBlocksPerChunk / GB;           // groups per chunk
     constexpr int SUB = sub_chunks(NMMA), SPS = packed_slots(NMMA), PSLOT = packed_slot_bytes(NMMA);
     constexpr int SB = b_slots(NMMA), SS = s_slots(NMMA);
@@ -143,12 +151,16 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
         for (int i = 0; i < 4; ++i) { mbar_init(bar(kFullP + i), 1); mbar_init(bar(kEmptyP + i), 4); }
         for (int i = 0; i < kSA; ++i) { mbar_init(bar(kReadyA + i), 4); mbar_init(bar(kFreeAB + i), 1); }
         for (int i = 0; i < 4; ++i) { mbar_init(bar(kFullB + i), 1); mbar_init(bar(kFreeB + i), 1); }
-        for (int i = 0; i < 4; ++i) { mbar_init(bar(kFullS + i), 1); mbar_init(bar(kEmptyS + i), 8); }
-        for (int i = 0; i < kSW; ++i) { mbar_init(bar(kFullW + i), 64); mbar_init(bar(kEmptyW + i), 8); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(kDFull + i), 1); mbar_init(bar(kDEmpty + i), 8); }
+        for (int i = 0; i < 4; ++i) { mbar_init(bar(kFullS + i), 1); mbar_init(bar(kEmptyS + i), kEpiWarps); }
+        for (int i = 0; i < kSW; ++i) { mbar_init(bar(kFullW + i), 64); mbar_init(bar(kEmptyW + i), kEpiWarps); }
+        for (int i = 0; i < kGroups; ++i) { mbar_init(bar(kDFull + i), 1); mbar_init(bar(kDEmpty + i), kEpiWarps); }
         *abort_flag = 0;
         mbar_fence_init();
     }
+    // the constant second K step of both operands (the MMA reads them through the async proxy)
+    for (int i = t; i < kRows * 4; i += kThreads) reinterpret_cast<uint32_t*>(smem + Smem::const_a(NMMA))[i] = 0x80808080u;
+    for (int i = t; i < NMMA * 4; i += kThreads) reinterpret_cast<uint32_t*>(smem + Smem::const_b(NMMA))[i] = 0x81818181u;
+    fence_proxy_async();
     if (warp == 0) {
         tmem_alloc(smem_u32(smem + Smem::kTmemPtr), 512);
         tmem_relinquish();
@@ -157,15 +169,6 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_ptr;
-    if (warp >= 4 && warp < 8) {
-        // every accumulator column of this thread's lane starts at the magic pattern
-        const uint32_t la = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        for (int c = 0; c < 512; c += 16) tmem_st16_const(la + c, (uint32_t)kMagicInt);
-        tmem_wait_st();
-        tc_fence_before();
-    }
-    __syncthreads();
-    tc_fence_after();
 
     if (warp == 0) {
         // ------------------------------------------------------------------------------------ producer
@@ -182,26 +185,41 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                     if (!wait(kEmptyS + ss, ((n / SS) & 1) ^ 1)) { ok = false; break; }
                     unsigned char* sslot = smem + s_off + ss * s_slot;
                     const unsigned char* xchunk = a.xb + (size_t)c * xb_chunk_bytes(NMMA);
-                    mbar_expect_tx(bar(kFullS + ss), s_slot);
-                    bulk_g2s_plain(smem_u32(sslot), xchunk + b_slot, s_slot, bar(kFullS + ss));
+                    if (a.ablate & 32) {
+                        mbar_arrive(bar(kFullS + ss));
+                    } else {
+                        mbar_expect_tx(bar(kFullS + ss), s_slot);
+                        bulk_g2s_plain(smem_u32(sslot), xchunk + b_slot, s_slot, bar(kFullS + ss));
+                    }
                     if (i % SUB == 0) {  // a new box: SUB chunks of packed nibbles at once
                         const int sp = np % SPS;
                         if (!wait(kEmptyP + sp, ((np / SPS) & 1) ^ 1)) { ok = false; break; }
-                        mbar_expect_tx(bar(kFullP + sp), PSLOT);
-                        tma_load_2d(smem_u32(smem + Smem::kPacked + sp * PSLOT), &map_w, c * (kKc / 2) / a.map_elem,
-                                    row0, bar(kFullP + sp));
+                        if (a.ablate & 4) {
+                            mbar_arrive(bar(kFullP + sp));
+                        } else {
+                            mbar_expect_tx(bar(kFullP + sp), PSLOT);
+                            tma_load_2d(smem_u32(smem + Smem::kPacked + sp * PSLOT), &map_w,
+                                        c * (kKc / 2) / a.map_elem, row0, bar(kFullP + sp));
+                        }
+                        TC_TL(0, np);
                         ++np;
                     }
                     if (!wait(kFreeB + sb, ((n / SB) & 1) ^ 1)) { ok = false; break; }
-                    mbar_expect_tx(bar(kFullB + sb), b_slot);
-                    bulk_g2s_plain(smem_u32(smem + Smem::b_off(NMMA) + sb * b_slot), xchunk, b_slot, bar(kFullB + sb));
+                    TC_TL(1, n);
+                    if (a.ablate & 16) {
+                        mbar_arrive(bar(kFullB + sb));
+                    } else {
+                        mbar_expect_tx(bar(kFullB + sb), b_slot);
+                        bulk_g2s_plain(smem_u32(smem + Smem::b_off(NMMA) + sb * b_slot), xchunk, b_slot, bar(kFullB + sb));
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = idesc_i8(2 * NMMA);
+            const uint32_t idesc = idesc_i8(NMMA);
+            const uint32_t const_a = smem_u32(smem + Smem::const_a(NMMA)), const_b = smem_u32(smem + Smem::const_b(NMMA));
             int gcount = 0, n = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
@@ -212,21 +230,23 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                     if (!wait(kReadyA + sa, (n / kSA) & 1)) { ok = false; break; }
                     if (!wait(kFullB + sb, (n / SB) & 1)) { ok = false; break; }
                     tc_fence_after();
+                    TC_TL(4, n);
                     const uint32_t a_base = smem_u32(smem + Smem::a_off(NMMA) + sa * kAStageBytes);
                     const uint32_t b_base = smem_u32(smem + Smem::b_off(NMMA) + sb * b_slot);
                     for (int g = 0; g < GPC && ok; ++g, ++gcount) {
-                        const int dg = gcount & 1;
-                        if (!wait(kDEmpty + dg, ((gcount >> 1) & 1) ^ 1)) { ok = false; break; }
+                        const int dg = gcount % kGroups;
+                        if (!wait(kDEmpty + dg, ((gcount / kGroups) & 1) ^ 1)) { ok = false; break; }
                         tc_fence_after();
-                        // one MMA per pair of k-blocks: A's two K steps are the two blocks' tiles, B's the pair layout
+                        TC_TL(5, gcount);
+                        // one MMA per k-block: K step 1 = the block, K step 2 = the constants
 #pragma unroll
-                        for (int bi = 0; bi < GB; bi += 2) {
+                        for (int bi = 0; bi < GB; ++bi) {
                             const int b = g * GB + bi;
                             const uint32_t a_addr = a_base + b * kABlockStride;
-                            const uint64_t da = smem_desc(a_addr, kABlockStride, 128);
-                            const uint32_t b_addr = b_base + (b >> 1) * 3 * NMMA * 16;
-                            const uint64_t db = smem_desc(b_addr, NMMA * 16, 128);
-                            tc_mma_i8(tmem + dg * 256 + bi * NMMA, da, db, idesc, 1u);
+                            const uint64_t da = smem_desc(a_addr, const_a - a_addr, 128);
+                            const uint32_t b_addr = b_base + b * NMMA * 16;
+                            const uint64_t db = smem_desc(b_addr, const_b - b_addr, 128);
+                            if (!(a.ablate & 8)) tc_mma_i8(tmem + dg * kGroupCols + bi * NMMA, da, db, idesc, 0u);
                         }
                         tc_commit(bar(kDFull + dg));
                     }
@@ -251,9 +271,10 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
             for (int i = 0; i < nloc; ++i, ++n) {
                 const int sw = n % kSW;
                 if (!wait(kEmptyW + sw, ((n / kSW) & 1) ^ 1)) { ok = false; break; }
+                if (lt == 0) TC_TL(10, n);
                 unsigned char* slot = smem + Smem::wscales(NMMA) + sw * kWScaleBytes;
 #pragma unroll
-                for (int rr = 0; rr < 2; ++rr) {
+                for (int rr = 0; rr < ((a.ablate & 64) ? 0 : 2); ++rr) {
                     const int r = lt * 2 + rr;
                     const int grow = min(tile * kRows + r, a.N - 1);
                     const uint32_t* src = reinterpret_cast<const uint32_t*>(a.Wsc + (size_t)grow * a.nkb) + (c0 + i) * 8;
@@ -267,9 +288,9 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                 cp_async_arrive(bar(kFullW + sw));
             }
         }
-    } else if (warp >= 12) {
+    } else if (warp >= 4 + kEpiWarps) {
         // ------------------------------------------------------------------------------------ unpack
-        const int ut = t - 384;  // 0..127
+        const int ut = t - (4 + kEpiWarps) * 32;  // 0..127
         int n = 0, np = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
@@ -281,6 +302,7 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
             const int sp = (np - 1) % SPS;
             if (sub == 0 && !wait(kFullP + sp, ((np - 1) / SPS) & 1)) { ok = false; break; }
             if (!wait(kFreeAB + sa, ((n / kSA) & 1) ^ 1)) { ok = false; break; }
+            if (ut == 0) TC_TL(2, n);
             const unsigned char* src = smem + Smem::kPacked + sp * PSLOT + sub * 128;
             unsigned char* dst = smem + Smem::a_off(NMMA) + sa * kAStageBytes;
             // All eight loads are issued before the first store: source and destination are both shared memory, so the
@@ -292,6 +314,7 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
             const int j = ut & 7, dg8 = (ut >> 3) & 7, rhi = ut >> 6;
             const int cc = (j + dg8) & 7;
             uint4 wv[8];
+            if (!(a.ablate & 2)) {
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
                 const int row = (rhi + 2 * it) * 8 + j;
@@ -309,9 +332,11 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                 *reinterpret_cast<uint4*>(d0) = o0;
                 *reinterpret_cast<uint4*>(d0 + kABlockStride) = o1;
             }
+            }
             // one arrival per warp: hundreds of per-thread arrivals on one barrier serialise in shared memory
             fence_proxy_async();
             __syncwarp();
+            if (ut == 0) TC_TL(3, n);
             if (lane == 0) {
                 mbar_arrive(bar(kReadyA + sa));
                 if (sub == SUB - 1 || i == nloc - 1) mbar_arrive(bar(kEmptyP + sp));  // the box is used up
@@ -321,23 +346,29 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
     } else if (warp >= 4) {
         // ------------------------------------------------------------------------------------ epilogue
         constexpr int CW = NMMA / 2;                            // sequences (columns of a block) per thread
-        const int half = (warp - 4) >> 2;                       // 0: sequences [0, CW), 1: [CW, NMMA)
+        constexpr int PW = CW < 16 ? CW : 16;                   // ... read and scaled in pieces of PW columns of
+        constexpr int PB = 32 / CW < 1 ? 1 : 32 / CW;           // PB consecutive k-blocks (32 values unless CW is 32)
+        constexpr int PP = CW / PW;                             // column pieces per k-block (2 for 64 sequences)
+        constexpr int NP = kBlocksPerChunk * PP / PB;           // pieces per chunk
+        static_assert(GB % PB == 0 && NP % 2 == 0 && (PP == 1 || PB == 1), "piece shape");
+        const int part = (warp - 4) >> 2;                       // sequences [part * CW, part * CW + CW)
         const int row = (warp & 3) * 32 + lane;                 // weight row of the tile = TMEM lane
-        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + half * CW;
-        int gcount = 0, n = 0;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + part * CW;
+        int gcount = 0, n = 0;                                  // accumulator groups / chunks consumed so far
         bool ok = true;
+        uint32_t v0[PB * PW], v1[PB * PW];                      // the piece being scaled and the one being read
         for (int u = blockIdx.x; u < units; u += gridDim.x) {
             int tile, kpart, c0, nloc;
             unit_range(u, tile, kpart, c0, nloc);
             const int row0 = tile * kRows;
-            float acc[CW];
+            unsigned long long acc2[CW / 2];                    // packed pairs of fp32 accumulators
 #pragma unroll
-            for (int j = 0; j < CW; ++j) acc[j] = 0.f;
-            for (int i = 0; i < nloc && ok; ++i, ++n) {
+            for (int j = 0; j < CW / 2; ++j) acc2[j] = 0ull;
+            for (int i = 0; i < nloc && ok; ++i, ++n, gcount += GPC) {
                 const int ss = n % SS;
                 const int sw = n % kSW;
-                if (!wait(kFullW + sw, (n / kSW) & 1)) { ok = false; break; }
-                uint32_t wcur[8];
+                ok = ok && wait(kFullW + sw, (n / kSW) & 1);
+                uint32_t wcur[8];                               // this row's 16 weight scales of the chunk
                 {
                     const uint4* wp = reinterpret_cast<const uint4*>(smem + Smem::wscales(NMMA) + sw * kWScaleBytes + row * 32);
                     const uint4 w0 = wp[0], w1 = wp[1];
@@ -346,73 +377,75 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(kEmptyW + sw));
-                if (!wait(kFullS + ss, (n / SS) & 1)) { ok = false; break; }
-                const float* sx = reinterpret_cast<const float*>(smem + s_off + ss * s_slot) + half * CW;
-#pragma unroll
-                for (int g = 0; g < GPC; ++g) {
-                    const int dg = gcount & 1;
-                    if (!wait(kDFull + dg, (gcount >> 1) & 1)) { ok = false; break; }
-                    ++gcount;
+                ok = ok && wait(kFullS + ss, (n / SS) & 1);
+                if (t == 128) TC_TL(6, n);
+                const float* sx = reinterpret_cast<const float*>(smem + s_off + ss * s_slot) + part * CW;
+                // Piece p of this chunk: k-blocks [b0, b0 + PB) with b0 = (p / PP) * PB, columns (p % PP) * PW.  Block b
+                // lives in accumulator group gcount + b / GB at columns (b % GB) * NMMA.
+                auto group_ready = [&](int b) {   // before the first read of a group: its MMAs have completed
+                    const int G = gcount + b / GB;
+                    ok = ok && wait(kDFull + G % kGroups, (G / kGroups) & 1);
                     tc_fence_after();
-                    // PB blocks of the group per wait (at least 32 accumulator words in flight, within the register budget)
-                    constexpr int PB = CW >= 32 ? 1 : 2;
+                    if (t == 128) TC_TL(7, G);
+                };
+                auto read_piece = [&](int p, uint32_t (&dst)[PB * PW]) {
+                    const int b0 = (p / PP) * PB;
+                    if (b0 % GB == 0 && p % PP == 0) group_ready(b0);
 #pragma unroll
-                    for (int bi = 0; bi < GB; bi += PB) {
-                        uint32_t v[PB][CW];
+                    for (int j = 0; j < PB; ++j) {
+                        const int b = b0 + j;
+                        tmem_ld_cols<PW>(lane_addr + ((gcount + b / GB) % kGroups) * kGroupCols + (b % GB) * NMMA + (p % PP) * PW,
+                                         *reinterpret_cast<uint32_t(*)[PW]>(&dst[j * PW]));
+                    }
+                };
+                // One piece: its values are in `cur` (read issued earlier).  Hand the accumulator group back after its
+                // last piece (before the next read is issued: the fence waits for reads in flight), start the read of the
+                // next piece into `nxt`, then scale and accumulate `cur`.
+                auto step = [&](int p, uint32_t (&cur)[PB * PW], uint32_t (&nxt)[PB * PW]) {
+                    const int b0 = (p / PP) * PB, h = p % PP;
+                    tmem_wait_ld();
+                    if (h == PP - 1 && (b0 + PB) % GB == 0) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(kDEmpty + (gcount + b0 / GB) % kGroups));
+                        if (t == 128) TC_TL(8, gcount + b0 / GB);
+                    }
+                    if (p + 1 < NP || i + 1 < nloc) read_piece(p + 1, nxt);   // p + 1 == NP: the unit's next chunk
+                    if (a.ablate & 1) { acc2[0] += cur[0]; return; }
 #pragma unroll
-                        for (int p = 0; p < PB; ++p) {
-                            const uint32_t addr = lane_addr + dg * 256 + (bi + p) * NMMA;
-                            if constexpr (CW == 8) {
-                                tmem_ld8(addr, v[p]);
-                            } else {
+                    for (int j = 0; j < PB; ++j) {
+                        const int b = b0 + j;
+                        const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&wcur[b >> 1]));
+                        const float w = (b & 1) ? wf.y : wf.x;
+                        const float W = w * kWScaleUp, CN = w * kOffsetTerm;   // both exact
 #pragma unroll
-                                for (int c = 0; c < CW; c += 16)
-                                    tmem_ld16(addr + c, *reinterpret_cast<uint32_t(*)[16]>(&v[p][c]));
-                            }
-                        }
-                        tmem_wait_ld();
-                        // hand the columns back holding the magic pattern
-#pragma unroll
-                        for (int p = 0; p < PB; ++p) {
-                            const uint32_t addr = lane_addr + dg * 256 + (bi + p) * NMMA;
-                            if constexpr (CW == 8) {
-                                tmem_st8_const(addr, (uint32_t)kMagicInt);
-                            } else {
-#pragma unroll
-                                for (int c = 0; c < CW; c += 16) tmem_st16_const(addr + c, (uint32_t)kMagicInt);
-                            }
-                        }
-                        if (bi == GB - PB) {  // the whole group is in registers and refilled: the MMA warp may go on
-                            tmem_wait_st();
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(bar(kDEmpty + dg));
-                        }
-#pragma unroll
-                        for (int p = 0; p < PB; ++p) {
-                            const int b = g * GB + bi + p;              // k-block within the chunk
-                            const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&wcur[b >> 1]));
-                            const float w = (b & 1) ? wf.y : wf.x;
-                            const float cn = -kMagicFloat * w;          // exact: a binary16 scale times 1.5 * 2^23
-#pragma unroll
-                            for (int q = 0; q < CW / 4; ++q) {
-                                const float4 s4 = *reinterpret_cast<const float4*>(sx + b * NMMA + 4 * q);
-                                float t0, t1, t2, t3;
-                                ffma2(t0, t1, __uint_as_float(v[p][4 * q + 0]), __uint_as_float(v[p][4 * q + 1]), w, w, cn, cn);
-                                ffma2(t2, t3, __uint_as_float(v[p][4 * q + 2]), __uint_as_float(v[p][4 * q + 3]), w, w, cn, cn);
-                                ffma2(acc[4 * q + 0], acc[4 * q + 1], t0, t1, s4.x, s4.y, acc[4 * q + 0], acc[4 * q + 1]);
-                                ffma2(acc[4 * q + 2], acc[4 * q + 3], t2, t3, s4.z, s4.w, acc[4 * q + 2], acc[4 * q + 3]);
-                            }
+                        for (int q = 0; q < PW / 4; ++q) {
+                            const ulonglong2 s4 = *reinterpret_cast<const ulonglong2*>(sx + b * NMMA + h * PW + 4 * q);
+                            scale_acc2(acc2[h * (PW / 2) + 2 * q], cur[j * PW + 4 * q], cur[j * PW + 4 * q + 1], W, CN, s4.x);
+                            scale_acc2(acc2[h * (PW / 2) + 2 * q + 1], cur[j * PW + 4 * q + 2], cur[j * PW + 4 * q + 3], W, CN, s4.y);
                         }
                     }
+                };
+                if (i == 0) read_piece(0, v0);   // nothing was read ahead across the unit boundary
+#pragma unroll
+                for (int p = 0; p < NP; p += 2) {
+                    step(p, v0, v1);
+                    step(p + 1, v1, v0);
                 }
                 __syncwarp();
-                if (ok && lane == 0) mbar_arrive(bar(kEmptyS + ss));
+                if (lane == 0) mbar_arrive(bar(kEmptyS + ss));
+                if (t == 128) TC_TL(9, n);
+            }
+            float acc[CW];
+#pragma unroll
+            for (int j = 0; j < CW / 2; ++j) {
+                acc[2 * j] = __uint_as_float((uint32_t)acc2[j]);
+                acc[2 * j + 1] = __uint_as_float((uint32_t)(acc2[j] >> 32));
             }
 
             // ---- results: straight to y, or through the K-split partial buffer with a last-arriver sum
             const int grow = row0 + row;
-            const int mbase = half * CW;
+            const int mbase = part * CW;
             if (a.ksplit == 1) {
                 if (grow < a.N && ok && !*abort_flag) {
 #pragma unroll
@@ -427,10 +460,10 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
 #pragma unroll
                 for (int j = 0; j < CW; ++j) mine[(mbase + j) * kRows + row] = acc[j];
                 __threadfence();
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
                 volatile int* last = reinterpret_cast<volatile int*>(smem + Smem::kLast);
                 if (t == 128) *last = (atomicAdd(&a.tickets[tile], 1u) == (unsigned)a.ksplit - 1) ? 1 : 0;
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
                 if (*last) {
                     __threadfence();
                     if (grow < a.N && !*abort_flag) {
@@ -442,7 +475,7 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                             a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
                         }
                     }
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
                     if (t == 128) a.tickets[tile] = 0;
                 }
             }
@@ -489,6 +522,8 @@ cudaError_t reserve_scratch(size_t bytes) {
 
 static int g_tc_ksplit_override = 0;
 void set_ksplit_override(int v) { g_tc_ksplit_override = v; }
+static int g_tc_ablate = 0;
+void set_ablate(int v) { g_tc_ablate = v; }
 
 bool eligible(const GemvArgs& a, int M) {
     if (M < 1 || M > 64 || a.K % 32 != 0 || a.K < 32) return false;
@@ -583,7 +618,10 @@ cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st) {
     t.partial = reinterpret_cast<float*>(scratch + part_off);
     t.tickets = reinterpret_cast<unsigned int*>(scratch);
     t.status = a.status;
-    t.N = a.N; t.M = M; t.Mpad = Mpad; t.nchunks = nchunks; t.ksplit = ksplit; t.map_elem = 4;
+    t.N = a.N; t.M = M; t.Mpad = Mpad; t.nchunks = nchunks; t.ksplit = ksplit; t.map_elem = 4; t.ablate = g_tc_ablate;
+#ifdef BW_GEMV_TIMELINE
+    t.timeline = static_cast<long long*>(debug_timeline_ptr());
+#endif
     const int grid = tiles * ksplit < sms ? tiles * ksplit : sms;  // persistent: one CTA per SM at most
     if (Mpad == 16) return launch_n<16>(map_w, t, grid, st);
     if (Mpad == 32) return launch_n<32>(map_w, t, grid, st);

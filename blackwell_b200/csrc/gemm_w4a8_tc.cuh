@@ -3,22 +3,34 @@
 //
 //   y[m][n] = sum_kb dot16(W[n,kb], xq[m,kb]) * w_sc[n,kb] * x_sc[m,kb]
 //
-// The scale changes every 16 k, the MMA consumes 32 k: each k-block gets its own MMA whose A operand holds the
-// block in its first 16-byte K core matrix and a shared all-zero core matrix in the second (the descriptor's
-// leading-dimension offset points the second K step at the zero region), so every accumulator tile is the exact
-// int32 dot product of ONE k-block.  Accumulator tiles start from the bit pattern of 1.5 * 2^23 (the epilogue stores
-// it back after every read), so the value read is a float holding 12582912 + 16 * dot exactly and the per-block
-// scaling is two FMAs per (row, sequence, block): t = fma(F, w_sc, -12582912 * w_sc) (exact for binary16
-// scales), acc = fma(t, x_sc/16, acc) -- issued as packed fp32x2 instructions, two sequences at a time.
+// The scale changes every 16 k, the MMA consumes 32 k: each k-block gets its own MMA (fresh accumulator, no
+// accumulation) whose first 16-byte K core matrix is the block and whose second is a constant shared by all blocks
+// (the descriptor's leading-dimension offset points there): -128 in every weight row, -127 in every sequence.  The
+// accumulator is then the int32  260096 + 16 * dot  -- never negative, because |16 * dot| <= 16 * 16 * 8 * 127 =
+// 260096 -- and below 2^23, so its bit pattern read as a float is the denormal (260096 + 16 * dot) * 2^-149 exactly:
+// no int-to-float conversion, no accumulator to re-arm.  The per-block scaling is two FMAs per (row, sequence, block):
+//   t = fma(F, w_sc * 2^110, -260096 * 2^-39 * w_sc)  =  16 * dot * w_sc * 2^-39      (a scalar FMA)
+//   acc = fma(t, x_sc / 16 * 2^39, acc)                                                (packed, two sequences)
+// (the powers of two keep every intermediate normal; the prep kernel stores x_sc / 16 * 2^39).  Scalar first stage
+// and packed second stage on purpose: the packed fp32 instruction issues only to half of the FMA pipe, so an
+// all-packed epilogue is bound by that half (measured: 48 % busy with the other half idle).
 //
-// Roles inside a persistent CTA of 12 warps (a work unit is 128 weight rows x a range of 256-k chunks):
+// Roles inside a persistent CTA of 16 warps (a work unit is 128 weight rows x a range of 256-k chunks):
 //   warp 0      producer: TMA 2-D loads of packed nibbles and weight scales, bulk copies of the activations
 //   warp 1      MMA issuer (one elected lane)
 //   warps 2-3   weight-scale loader: cp.async of each row's 16 scales per chunk into a ring, eight chunks ahead
 //   warps 4-11  epilogue: tcgen05.ld, scaling, fp32 accumulation in registers, final store (thread = weight row
-//               = TMEM lane; warps 4-7 take the first half of the sequences, warps 8-11 the second, so that
-//               every scheduler has two epilogue warps to overlap and each thread keeps half the accumulators)
+//               = TMEM lane; warps 4-7 take the first half of the sequences, warps 8-11 the second).  Accumulators are
+//               read in pieces of 32 values (16 for 64 sequences) and the read of the next piece is issued before the
+//               arithmetic of the current one: a tensor-memory read takes 100-150 cycles to return and only one batch
+//               of reads can be in flight per warp (tcgen05.wait::ld has no count).
 //   warps 12-15 unpack: nibbles -> signed bytes 16*q in the K-major core-matrix layout the MMA reads
+// Measured on the 151,643 x 4096 matrix (tuning key 19 switches parts off): 16 / 32 / 64 sequences take 228 / 338 /
+// 498 us; without the scaling arithmetic 181 / 221 / 399; with nothing but the barrier traffic and the accumulator
+// reads 90 / 134 / 327.  The kernel is bound by the latency chain of the epilogue warps (issue slots 50 % busy, no
+// pipe above 70 %), not by HBM (weights alone would take 58 us) or the tensor pipe (6 % busy).  Tried and measured
+// slower: 16 epilogue warps with a quarter of the sequences each (545 us at 64 sequences: 80 registers, spills), a
+// ring of four accumulator groups (616), all-scalar arithmetic (547), 32-column reads at 64 sequences (534).
 // All waits are bounded; a wait that gives up raises an abort flag that every role polls.
 #pragma once
 #include <cuda.h>
@@ -40,7 +52,8 @@ constexpr int kABlockStride = 2048 + 16;  // bytes between the int8 tiles of con
 constexpr int kPackedBytes = kRows * (kKc / 2);                  // 16384
 constexpr int kWScaleBytes = kRows * kBlocksPerChunk * 2;        // 4096
 constexpr int kAStageBytes = kBlocksPerChunk * kABlockStride;    // 33024
-constexpr int kThreads = 512;
+constexpr int kEpiWarps = 8;     // epilogue warps: two per TMEM lane quarter, each half of the sequences
+constexpr int kThreads = (4 + kEpiWarps + 4) * 32;   // + producer, MMA issuer, two scale-loader and four unpack warps
 
 struct TcArgs {
     float* y;                 // [M][y_stride]
@@ -56,13 +69,18 @@ struct TcArgs {
     int nchunks;              // ceil(K / 256)
     int ksplit;               // CTAs sharing one row tile
     int map_elem;             // bytes per element of the weight tensor map (its x coordinate is in elements)
+#ifdef BW_GEMV_TIMELINE
+    long long* timeline;      // experiment builds only: SM-clock stamps of CTA 0's roles, [slot][256]
+#endif
+    int ablate;               // measurement only (tuning key 19): 1 no epilogue math, 2 no unpack, 4 no weight loads, 8 no MMAs
 };
 
-// B operand of one chunk: 8 block pairs, each [block 2p: Mpad rows x 16 B][Mpad rows of zeros][block 2p + 1].
-// One MMA (K = 32) takes a pair: its first K step reads rows [0, 2 Mpad) from the start of the pair (block 2p, then
-// the zeros), its second K step the same number of rows starting at the zeros (zeros, then block 2p + 1), so the
-// accumulator columns [0, Mpad) hold the dots of block 2p and [Mpad, 2 Mpad) those of block 2p + 1.
-__host__ __device__ constexpr int b_chunk_bytes(int Mpad) { return (kBlocksPerChunk / 2) * 3 * Mpad * 16; }
+// B operand of one chunk: 16 blocks of [Mpad sequences x 16 B]; the MMA's second K step reads the shared constant.
+constexpr int kOffsetInt = 260096;                 // 16 (k) x (-128) x (-127): what the constant K step adds
+constexpr float kWScaleUp = 0x1p110f;              // first-stage factor:  w_sc * 2^110 (binary16 scales stay finite)
+constexpr float kXScaleUp = 0x1p39f;               // second-stage factor: x_sc / 16 * 2^39
+constexpr float kOffsetTerm = -260096.0f * 0x1p-39f;  // times w_sc: cancels the constant K step
+__host__ __device__ constexpr int b_chunk_bytes(int Mpad) { return kBlocksPerChunk * Mpad * 16; }
 // bytes of one activation chunk in global memory: the B operand, then 16 x Mpad block scales
 __host__ __device__ inline size_t xb_chunk_bytes(int Mpad) { return (size_t)b_chunk_bytes(Mpad) + (size_t)kBlocksPerChunk * Mpad * 4; }
 
@@ -104,26 +122,43 @@ __device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&v)[8]) {
                  : "r"(addr)
                  : "memory");
 }
-__device__ __forceinline__ void tmem_st8_const(uint32_t addr, uint32_t c) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(addr), "r"(c) : "memory");
+__device__ __forceinline__ void tmem_ld4(uint32_t addr, uint32_t (&v)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                 : "r"(addr)
+                 : "memory");
 }
-__device__ __forceinline__ void tmem_st16_const(uint32_t addr, uint32_t c) {
+// acc (two packed fp32) += {fma(f0, W, CN), fma(f1, W, CN)} * xs2 (two packed fp32): the two scaling stages of one
+// k-block for two sequences.  f0 / f1 are accumulator words read as (denormal) floats.
+__device__ __forceinline__ void scale_acc2(unsigned long long& acc, uint32_t f0, uint32_t f1, float W, float CN,
+                                           unsigned long long xs2) {
+    asm("{\n\t.reg .f32 t0, t1;\n\t.reg .b64 tt;\n\t"
+        "fma.rn.f32 t0, %1, %3, %4;\n\t"
+        "fma.rn.f32 t1, %2, %3, %4;\n\t"
+        "mov.b64 tt, {t0, t1};\n\t"
+        "fma.rn.f32x2 %0, tt, %5, %0;\n\t}"
+        : "+l"(acc)
+        : "f"(__uint_as_float(f0)), "f"(__uint_as_float(f1)), "f"(W), "f"(CN), "l"(xs2));
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
-        ::"r"(addr), "r"(c)
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(addr)
         : "memory");
 }
-// Two fp32 FMAs in one instruction (sm_100 packed single precision): d = a * b + c lane-wise on register pairs.
-__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
-    unsigned long long A, B, C, D;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(A) : "f"(a0), "f"(a1));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(B) : "f"(b0), "f"(b1));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(C) : "f"(c0), "f"(c1));
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(D) : "l"(A), "l"(B), "l"(C));
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(D));
+template <int CW>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t addr, uint32_t (&v)[CW]) {
+    if constexpr (CW == 4) tmem_ld4(addr, v);
+    else if constexpr (CW == 8) tmem_ld8(addr, v);
+    else if constexpr (CW == 16) tmem_ld16(addr, v);
+    else tmem_ld32(addr, v);
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // 2-D tiled TMA load (no multicast): box -> shared memory of this CTA, bytes counted on an mbarrier.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {

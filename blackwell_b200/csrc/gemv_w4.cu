@@ -27,6 +27,7 @@ cudaError_t launch(const GemvArgs& a, int M, cudaStream_t st);
 cudaError_t reserve_scratch(size_t bytes);
 size_t scratch_bytes(int M, int N, int K);
 void set_ksplit_override(int v);
+void set_ablate(int v);
 }  // namespace tc
 
 // --------------------------------------------------------------------------
@@ -133,6 +134,7 @@ static std::atomic<int> g_tune_mma_pack{1};
 #ifdef BW_GEMV_TIMELINE
 static unsigned long long* g_timeline_ptr = nullptr;
 extern "C" void bw_debug_set_timeline(void* dev_ptr) { g_timeline_ptr = static_cast<unsigned long long*>(dev_ptr); }
+void* debug_timeline_ptr() { return g_timeline_ptr; }
 #endif
 static std::atomic<int> g_tune_mma_slab{0}, g_tune_mma_min{0}, g_tune_mma_max{0}, g_tune_mma_stages{0};
 static std::atomic<long long> g_launches{0};
@@ -656,6 +658,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 16: g_tune_shrink_ring = value; return 0;
         case 17: g_tune_mma_mode = value; return 0;
         case 18: g_tune_mma_pack = value; return 0;
+        case 19: tc::set_ablate(value); return 0;
         default: return cudaErrorInvalidValue;
     }
 }

@@ -78,18 +78,24 @@ def test_decode_step_matches_cpu_chain(cuda, M):
         x = x + cpu_gemv(act, *hw.np[sd + 4])
     logits = cpu_gemv(oracle.rmsnorm(x, eng.rn_final.cpu().numpy()), *hw.np[5 + 900001])
 
-    # a rounding tie of the int8 activation quantizer resolved the other way (rsqrtf, summation order) moves one
-    # element by a whole step; with 16 sequences such flips are five times as likely as with 3
-    tol = 2e-3 if M <= 3 else 5e-3
-    assert max_abs_rel(eng.x.cpu().numpy(), x) < tol
-    assert max_abs_rel(eng.logits.cpu().numpy(), logits) < tol
+    # A rounding tie of the int8 activation quantizer resolved the other way (rsqrtf, summation order) moves one
+    # element by a whole step and with it one sequence's later values by up to a percent of the largest one; every
+    # other sequence agrees to fp32 rounding.  So: all sequences inside the loose bound, all but a few inside the tight.
+    def per_seq(a, b):
+        return np.abs(a.astype(np.float64) - b).max(axis=1) / np.abs(b).max()
+
+    ex, el = per_seq(eng.x.cpu().numpy(), x), per_seq(eng.logits.cpu().numpy(), logits)
+    print("per-sequence max abs rel: x", np.array2string(ex, precision=2), "logits", np.array2string(el, precision=2))
+    tol = 2e-2
+    assert ex.max() < tol and el.max() < tol, (ex, el)
+    assert (el > 1e-4).sum() <= max(1, M // 4), el
     got_k = eng.kc.cpu().numpy().reshape(M, s.layers, nkv, max_seq, 128).astype(np.float32)
-    assert max_abs_rel(got_k, Kc.astype(np.float32)) < tol
+    assert max_abs_rel(got_k, Kc.astype(np.float32)) < 5e-3
     # greedy ids: equal wherever the CPU's top-2 margin exceeds the numerical noise
     ids = eng.tokens.cpu().numpy()
     for m in range(M):
         top = np.sort(logits[m])[-2:]
-        if top[1] - top[0] > 1e-2 * np.abs(logits[m]).max():
+        if top[1] - top[0] > (2.5 * el[m] + 1e-4) * np.abs(logits).max():
             assert ids[m] == int(np.argmax(logits[m]))
     assert np.array_equal(eng.pos.cpu().numpy(), pos0 + 1)
 
