@@ -417,12 +417,12 @@ gemm_w4a8_tc_kernel(const __grid_constant__ CUtensorMap map_w, const TcArgs a) {
                         const int b = b0 + j;
                         const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&wcur[b >> 1]));
                         const float w = (b & 1) ? wf.y : wf.x;
-                        const float W = w * kWScaleUp, CN = w * kOffsetTerm;   // both exact
+                        const unsigned long long W2 = pack2(w * kWScaleUp), CN2 = pack2(w * kOffsetTerm);   // both exact
 #pragma unroll
                         for (int q = 0; q < PW / 4; ++q) {
                             const ulonglong2 s4 = *reinterpret_cast<const ulonglong2*>(sx + b * NMMA + h * PW + 4 * q);
-                            scale_acc2(acc2[h * (PW / 2) + 2 * q], cur[j * PW + 4 * q], cur[j * PW + 4 * q + 1], W, CN, s4.x);
-                            scale_acc2(acc2[h * (PW / 2) + 2 * q + 1], cur[j * PW + 4 * q + 2], cur[j * PW + 4 * q + 3], W, CN, s4.y);
+                            scale_acc2(acc2[h * (PW / 2) + 2 * q], cur[j * PW + 4 * q], cur[j * PW + 4 * q + 1], W2, CN2, s4.x);
+                            scale_acc2(acc2[h * (PW / 2) + 2 * q + 1], cur[j * PW + 4 * q + 2], cur[j * PW + 4 * q + 3], W2, CN2, s4.y);
                         }
                     }
                 };

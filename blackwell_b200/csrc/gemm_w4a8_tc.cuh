@@ -9,11 +9,12 @@
 // accumulator is then the int32  260096 + 16 * dot  -- never negative, because |16 * dot| <= 16 * 16 * 8 * 127 =
 // 260096 -- and below 2^23, so its bit pattern read as a float is the denormal (260096 + 16 * dot) * 2^-149 exactly:
 // no int-to-float conversion, no accumulator to re-arm.  The per-block scaling is two FMAs per (row, sequence, block):
-//   t = fma(F, w_sc * 2^110, -260096 * 2^-39 * w_sc)  =  16 * dot * w_sc * 2^-39      (a scalar FMA)
-//   acc = fma(t, x_sc / 16 * 2^39, acc)                                                (packed, two sequences)
-// (the powers of two keep every intermediate normal; the prep kernel stores x_sc / 16 * 2^39).  Scalar first stage
-// and packed second stage on purpose: the packed fp32 instruction issues only to half of the FMA pipe, so an
-// all-packed epilogue is bound by that half (measured: 48 % busy with the other half idle).
+//   t = fma(F, w_sc * 2^110, -260096 * 2^-39 * w_sc)  =  16 * dot * w_sc * 2^-39
+//   acc = fma(t, x_sc / 16 * 2^39, acc)
+// (the powers of two keep every intermediate normal; the prep kernel stores x_sc / 16 * 2^39), both issued as packed
+// fp32x2 instructions, two sequences at a time.  The packed instruction issues to half of the FMA pipe only; a scalar
+// first stage (which can use the other half) and an all-scalar epilogue both measured slower (498 and 547 us against
+// 482 us at 64 sequences): the epilogue is short of issue slots and latency hiding, not of FMA throughput.
 //
 // Roles inside a persistent CTA of 16 warps (a work unit is 128 weight rows x a range of 256-k chunks):
 //   warp 0      producer: TMA 2-D loads of packed nibbles and weight scales, bulk copies of the activations
@@ -25,12 +26,12 @@
 //               arithmetic of the current one: a tensor-memory read takes 100-150 cycles to return and only one batch
 //               of reads can be in flight per warp (tcgen05.wait::ld has no count).
 //   warps 12-15 unpack: nibbles -> signed bytes 16*q in the K-major core-matrix layout the MMA reads
-// Measured on the 151,643 x 4096 matrix (tuning key 19 switches parts off): 16 / 32 / 64 sequences take 228 / 338 /
-// 498 us; without the scaling arithmetic 181 / 221 / 399; with nothing but the barrier traffic and the accumulator
+// Measured on the 151,643 x 4096 matrix (tuning key 19 switches parts off): 16 / 32 / 64 sequences take 227 / 331 /
+// 482 us; without the scaling arithmetic 182 / 219 / 347; with nothing but the barrier traffic and the accumulator
 // reads 90 / 134 / 327.  The kernel is bound by the latency chain of the epilogue warps (issue slots 50 % busy, no
 // pipe above 70 %), not by HBM (weights alone would take 58 us) or the tensor pipe (6 % busy).  Tried and measured
 // slower: 16 epilogue warps with a quarter of the sequences each (545 us at 64 sequences: 80 registers, spills), a
-// ring of four accumulator groups (616), all-scalar arithmetic (547), 32-column reads at 64 sequences (534).
+// ring of four accumulator groups (616), 32-column reads at 64 sequences (534).
 // All waits are bounded; a wait that gives up raises an abort flag that every role polls.
 #pragma once
 #include <cuda.h>
@@ -128,35 +129,28 @@ __device__ __forceinline__ void tmem_ld4(uint32_t addr, uint32_t (&v)[4]) {
                  : "r"(addr)
                  : "memory");
 }
-// acc (two packed fp32) += {fma(f0, W, CN), fma(f1, W, CN)} * xs2 (two packed fp32): the two scaling stages of one
-// k-block for two sequences.  f0 / f1 are accumulator words read as (denormal) floats.
-__device__ __forceinline__ void scale_acc2(unsigned long long& acc, uint32_t f0, uint32_t f1, float W, float CN,
-                                           unsigned long long xs2) {
-    asm("{\n\t.reg .f32 t0, t1;\n\t.reg .b64 tt;\n\t"
-        "fma.rn.f32 t0, %1, %3, %4;\n\t"
-        "fma.rn.f32 t1, %2, %3, %4;\n\t"
-        "mov.b64 tt, {t0, t1};\n\t"
-        "fma.rn.f32x2 %0, tt, %5, %0;\n\t}"
-        : "+l"(acc)
-        : "f"(__uint_as_float(f0)), "f"(__uint_as_float(f1)), "f"(W), "f"(CN), "l"(xs2));
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(addr)
-        : "memory");
-}
 template <int CW>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t addr, uint32_t (&v)[CW]) {
+    static_assert(CW == 4 || CW == 8 || CW == 16, "columns per read");
     if constexpr (CW == 4) tmem_ld4(addr, v);
     else if constexpr (CW == 8) tmem_ld8(addr, v);
-    else if constexpr (CW == 16) tmem_ld16(addr, v);
-    else tmem_ld32(addr, v);
+    else tmem_ld16(addr, v);
+}
+// acc (two packed fp32) += ({f0, f1} * W2 + CN2) * xs2: the two scaling stages of one k-block for two sequences, both
+// as packed fp32 instructions.  f0 / f1 are accumulator words read as (denormal) floats; W2 = {W, W}, CN2 = {CN, CN}.
+__device__ __forceinline__ void scale_acc2(unsigned long long& acc, uint32_t f0, uint32_t f1, unsigned long long W2,
+                                                  unsigned long long CN2, unsigned long long xs2) {
+    asm("{\n\t.reg .b64 ff, tt;\n\t"
+        "mov.b64 ff, {%1, %2};\n\t"
+        "fma.rn.f32x2 tt, ff, %3, %4;\n\t"
+        "fma.rn.f32x2 %0, tt, %5, %0;\n\t}"
+        : "+l"(acc)
+        : "r"(f0), "r"(f1), "l"(W2), "l"(CN2), "l"(xs2));
+}
+__device__ __forceinline__ unsigned long long pack2(float a) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(a));
+    return r;
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
