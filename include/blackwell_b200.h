@@ -46,15 +46,15 @@ int bw_gemv_int4_warp(float* y_out, const void* x_packed, const float* x_scale, 
 /* W4A8 GEMV: int8 activations (from bw_quantize_int8*), binary16 weight scales
  * (passed as uint16_t bit patterns).  Extension; arithmetic follows
  * src/kernels/gemv_int8.cu:937-965 with the int8 operand of :718-748.
- * Any M >= 1.  Batch routing of all bw_gemv_w4a8* entry points: up to 7 sequences run in the streaming dp4a
- * kernel; from 8 sequences on (K % 32 == 0, 16-byte aligned W and x) the tcgen05 kernel takes 64 sequences per
- * launch; operands the tensor-core kernel cannot take fall back to dp4a passes of 8 (pre-quantized x only). */
+ * Any M >= 1.  Batch routing of all bw_gemv_w4a8* entry points (by measurement; bw_set_tuning keys 5, 13, 14 move
+ * the borders): up to 4 sequences run in the streaming dp4a kernel, 5 to 16 in the streaming mma.sync kernel, more
+ * than 16 (K % 32 == 0, 16-byte aligned W and x) in the tcgen05 kernel, 64 sequences per launch; operands the
+ * tensor-core kernel cannot take fall back to passes of 16 through the mma.sync kernel (or 8 through dp4a). */
 int bw_gemv_w4a8(float* y_out, const int8_t* x_q, const float* x_scale, const uint8_t* W_packed,
                  const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
 
 /* W4A8 GEMV with the activation quantizer fused into the prologue: x is
- * binary16 [M][K].  K % 32 == 0, 16-byte aligned pointers; any M >= 1 (see the routing note above; M > 8
- * needs the tensor-core path's operand alignment, else cudaErrorInvalidValue). */
+ * binary16 [M][K].  K % 32 == 0, 16-byte aligned pointers; any M >= 1 (see the routing note above). */
 int bw_gemv_w4a8_f16in(float* y_out, const uint16_t* x_f16, const uint8_t* W_packed, const uint16_t* W_scale_f16,
                        int K, int N, int M, void* stream);
 
@@ -333,7 +333,7 @@ int bw_peer_comm_status(void* comm, int* status_out);
 int bw_peer_comm_destroy(void* comm);
 
 /* Library-owned scratch memory.  Two kernel families keep a per-device, grow-only scratch block: the tensor-core
- * GEMV (batches of 8 sequences and more through bw_gemv_w4a8*: prepared activations, K-split partial sums, arrival
+ * GEMV (batches of more than 16 sequences through bw_gemv_w4a8*: prepared activations, K-split partial sums, arrival
  * counters) and the allocating attention entry points (split partials, arrival counters).  A block is shared by all
  * streams of the device -- two calls of the same family must not overlap on one GPU -- and grows (cudaMalloc +
  * cudaMemset, synchronising) when a larger problem arrives; an outgrown block stays allocated until the library is
@@ -358,7 +358,9 @@ int bw_reserve_scratch(size_t gemv_bytes, size_t attention_bytes);
  * 16; a smallest batch above 16 switches it off), key 15 = its ring stages (0 = automatic), key 16 = shrink the
  * small-batch kernel's ring to the tiles a CTA has (1, default) or not (0), key 17 = timing experiments on the
  * mma.sync kernel (0 = off; 1 = skip its arithmetic, 2 = skip its copies: results are then meaningless), key 18 =
- * its packed form for up to 4 sequences on (1, default) / off (0). */
+ * its packed form for up to 4 sequences on (1, default) / off (0), key 19 = timing experiments on the tcgen05
+ * kernel (0 = off; bits: 1 no epilogue arithmetic, 2 no unpack, 4 no weight loads, 8 no MMAs, 16 / 32 no activation /
+ * activation-scale copies, 64 no weight-scale loads: results are then meaningless). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);
