@@ -64,6 +64,47 @@ __global__ void __launch_bounds__(256) prep_x_kernel(unsigned char* xb, const Ge
     reinterpret_cast<float*>(chunk + (size_t)b_chunk_bytes(Mpad))[b * Mpad + m] = s * kXScaleUp;
 }
 
+// The same quantize for the streaming kernels (3 to 16 sequences): plain int8 [M][K] and fp32 scales [M][K/16], the
+// layout of pre-quantized activations.  Without it every CTA of the GEMV quantizes all M x K activations itself
+// (RMSNorm or SwiGLU included), which at 8 sequences costs more than the weight stream of the per-layer matrices
+// (measured, 8B shape, 8 sequences: QKV 18.6 -> 10.0 us, gate+up 31.1 -> 22.6, down with SwiGLU 45.5 -> 18.4 without the
+// prologue).  Grid (ceil(K / 16 / 256), M), 256 threads; starts early under programmatic dependent launch.
+__global__ void __launch_bounds__(256) prep_plain_kernel(int8_t* xq, float* xs, const GemvArgs a, int M) {
+    __shared__ float part[8];
+    __shared__ float rstd_s;
+    pdl_trigger();
+    pdl_wait();   // the activations come from the kernel before
+    const int m = blockIdx.y, t = threadIdx.x;
+    const int nkb = a.K / 16;
+    float rstd = 1.f;
+    if (a.xkind == kXFloatNorm) {
+        float ss = 0.f;
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * a.x_stride);
+        for (int i = t; i < a.K / 4; i += 256) {
+            const float4 f = __ldg(p + i);
+            ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); ss = fmaf(f.z, f.z, ss); ss = fmaf(f.w, f.w, ss);
+        }
+        ss = warp_sum(ss);
+        if ((t & 31) == 0) part[t >> 5] = ss;
+        __syncthreads();
+        if (t == 0) {
+            float tot = 0.f;
+            for (int w = 0; w < 8; ++w) tot += part[w];
+            rstd_s = rsqrtf(tot / (float)a.K + a.eps);
+        }
+        __syncthreads();
+        rstd = rstd_s;
+    }
+    const int kb = blockIdx.x * 256 + t;
+    if (kb >= nkb) return;
+    uint32_t e[2], o[2];
+    float s;
+    make_xblock(a, m, kb, rstd, e, o, s);   // even-k / odd-k bytes and scale / 16
+    *reinterpret_cast<uint4*>(xq + (size_t)m * a.K + 16 * (size_t)kb) =
+        make_uint4(prmt(e[0], o[0], 0x5140), prmt(e[0], o[0], 0x7362), prmt(e[1], o[1], 0x5140), prmt(e[1], o[1], 0x7362));
+    xs[(size_t)m * nkb + kb] = s * 16.0f;
+}
+
 // ----------------------------------------------------------------------------------------------------------
 // Shared memory map of the MMA kernel (offsets from the 1024-aligned base).
 // ----------------------------------------------------------------------------------------------------------
@@ -520,6 +561,28 @@ cudaError_t reserve_scratch(size_t bytes) {
     return bytes ? g_tc_scratch.get(bytes, (size_t)16 << 20, nullptr, &p) : cudaSuccess;
 }
 
+constexpr size_t kTicketBytes = 65536;  // arrival counters: 16,384 row tiles; larger matrices are not K-split
+
+// Quantizes the activations of a streaming-kernel call once (see prep_plain_kernel) into the scratch block and returns
+// the pre-quantized operand.  Calls that go on to the tensor-core kernel do not use this (its own prep writes the same
+// region).
+cudaError_t prepare_plain(const GemvArgs& a, int M, cudaStream_t st, const int8_t** xq_out, const float** xs_out) {
+    const size_t q_bytes = ((size_t)M * a.K + 255) & ~(size_t)255;
+    const size_t s_bytes = (size_t)M * (a.K / 16) * sizeof(float);
+    unsigned char* scratch = nullptr;
+    cudaError_t e = g_tc_scratch.get(kTicketBytes + q_bytes + s_bytes, (size_t)16 << 20, st, &scratch);
+    if (e != cudaSuccess) return e;
+    int8_t* xq = reinterpret_cast<int8_t*>(scratch + kTicketBytes);
+    float* xs = reinterpret_cast<float*>(scratch + kTicketBytes + q_bytes);
+    const dim3 grid((a.K / 16 + 255) / 256, M);
+    e = launch_pdl(prep_plain_kernel, grid, dim3(256), 0, st, xq, xs, a, M);
+    count_launch(1);
+    if (e != cudaSuccess) return e;
+    *xq_out = xq;
+    *xs_out = xs;
+    return cudaPeekAtLastError();
+}
+
 static int g_tc_ksplit_override = 0;
 void set_ksplit_override(int v) { g_tc_ksplit_override = v; }
 static int g_tc_ablate = 0;
@@ -549,7 +612,6 @@ static cudaError_t launch_n(const CUtensorMap& map_w, const TcArgs& t, int grid,
 }
 
 // Launch geometry and scratch layout of one call: [tickets][activation chunks][K-split partials].
-constexpr size_t kTicketBytes = 65536;  // 16,384 row tiles; larger matrices are not K-split
 
 struct TcLayout {
     int Mpad, nchunks, tiles, ksplit;
@@ -578,7 +640,8 @@ static TcLayout tc_layout(int M, int N, int K) {
 size_t scratch_bytes(int M, int N, int K) {
     if (M < 1 || N < 1 || K < 32) return 0;
     const TcLayout l = tc_layout(M < 64 ? M : 64, N, K);
-    return l.part_off + l.part_bytes;
+    const size_t plain = kTicketBytes + (((size_t)M * K + 255) & ~(size_t)255) + (size_t)M * (K / 16) * sizeof(float);
+    return l.part_off + l.part_bytes > plain ? l.part_off + l.part_bytes : plain;
 }
 
 // y = W . q8(prologue(x)) for 1..64 sequences on the tensor cores.  `a` carries the operands as for the streaming

@@ -28,6 +28,7 @@ cudaError_t reserve_scratch(size_t bytes);
 size_t scratch_bytes(int M, int N, int K);
 void set_ksplit_override(int v);
 void set_ablate(int v);
+cudaError_t prepare_plain(const GemvArgs& a, int M, cudaStream_t st, const int8_t** xq_out, const float** xs_out);
 }  // namespace tc
 
 // --------------------------------------------------------------------------
@@ -131,6 +132,7 @@ static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0},
 static std::atomic<int> g_tune_shrink_ring{1};
 static std::atomic<int> g_tune_mma_mode{0};
 static std::atomic<int> g_tune_mma_pack{1};
+static std::atomic<int> g_tune_prep_min{0};
 #ifdef BW_GEMV_TIMELINE
 static unsigned long long* g_timeline_ptr = nullptr;
 extern "C" void bw_debug_set_timeline(void* dev_ptr) { g_timeline_ptr = static_cast<unsigned long long*>(dev_ptr); }
@@ -433,18 +435,32 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
     // activations need several windows of K are faster on the tcgen05 kernel).
     const int mma_min = g_tune_mma_min.load() > 0 ? g_tune_mma_min.load() : 5;
     const int mma_max = g_tune_mma_max.load() > 0 ? g_tune_mma_max.load() : 16;
-    if (M >= mma_min && M <= mma_max && M <= 16) {
-        mma::MmaPlan mp;
-        if (plan_mma(a, M, (int)sizeof(WS), mp)) {
-            const bool windows = mp.win_cols < a.K / 32;
-            const bool tc_can = sizeof(WS) == 2 && M > 8 && tc::eligible(a, M);
-            const bool forced = g_tune_mma_min.load() > 0;  // an explicit range (tests, experiments) takes the kernel as it is
-            if (forced || !(windows && tc_can)) return launch_mma<WS>(a, mp, M, st);
-        }
-    }
-    // Larger batches go to the tcgen05 kernel, up to 64 sequences per launch.
     const int tc_min = g_tune_tc_min.load() > 0 ? g_tune_tc_min.load() : 8;
-    if (sizeof(WS) == 2 && M >= tc_min && tc::eligible(a, M < 64 ? M : 64)) {
+    mma::MmaPlan mp;
+    bool use_mma = false;
+    if (M >= mma_min && M <= mma_max && M <= 16 && plan_mma(a, M, (int)sizeof(WS), mp)) {
+        const bool windows = mp.win_cols < a.K / 32;
+        const bool tc_can = sizeof(WS) == 2 && M > 8 && tc::eligible(a, M);
+        const bool forced = g_tune_mma_min.load() > 0;  // an explicit range (tests, experiments) takes the kernel as it is
+        use_mma = forced || !(windows && tc_can);
+    }
+    const bool use_tc = !use_mma && sizeof(WS) == 2 && M >= tc_min && tc::eligible(a, M < 64 ? M : 64);
+    // From 3 sequences on, a call of a streaming kernel with an int8 prologue (f16 / f32 / RMSNorm / SwiGLU input) has
+    // its activations quantized once by a small kernel instead of once per CTA; the GEMV then runs on the result as on
+    // any pre-quantized operand (same quantize code, same bits).
+    const int prep_min = g_tune_prep_min.load() > 0 ? g_tune_prep_min.load() : 3;
+    if (!use_tc && M >= prep_min && a.K % 32 == 0 &&
+        (a.xkind == kXHalf || a.xkind == kXFloat || a.xkind == kXFloatNorm || a.xkind == kXSwiglu)) {
+        const int8_t* xq = nullptr;
+        const float* xs = nullptr;
+        cudaError_t e = tc::prepare_plain(a, M, st, &xq, &xs);
+        if (e != cudaSuccess) return e;
+        a.x = xq; a.xsc = xs; a.x2 = nullptr; a.norm_w = nullptr; a.xkind = kXInt8; a.x_stride = a.K;
+        if (use_mma && !plan_mma(a, M, (int)sizeof(WS), mp)) use_mma = false;   // the plan depends on the operand kind
+    }
+    if (use_mma) return launch_mma<WS>(a, mp, M, st);
+    // Larger batches go to the tcgen05 kernel, up to 64 sequences per launch.
+    if (use_tc) {
         for (int m0 = 0; m0 < M; m0 += 64) {
             const int mc = (M - m0) < 64 ? (M - m0) : 64;
             GemvArgs b = a;
@@ -659,6 +675,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 17: g_tune_mma_mode = value; return 0;
         case 18: g_tune_mma_pack = value; return 0;
         case 19: tc::set_ablate(value); return 0;
+        case 20: g_tune_prep_min = value; return 0;
         default: return cudaErrorInvalidValue;
     }
 }
