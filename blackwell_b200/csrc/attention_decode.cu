@@ -21,6 +21,7 @@
 #include "attention_mma.cuh"
 #include "common.cuh"
 #include "host_util.h"
+#include "quant_rules.cuh"
 #include "rope_norm.cuh"
 
 namespace bw {
@@ -57,7 +58,38 @@ struct AttnArgs {
     const float* q_norm_w;
     const float* k_norm_w;
     float eps, rope_base;
+    // optional second output (tensor-core kernel): the result block-16 quantized to int8 with the reference's rule,
+    // i8 [M][nqh][128] + f32 scales [M][nqh][8] -- what the O projection's GEMV takes as pre-quantized activations
+    int8_t* out_q;
+    float* out_qs;
 };
+
+// Final outputs of one head, four consecutive dimensions per lane (whole warp): float and / or quantized.
+__device__ __forceinline__ void emit_head4(const AttnArgs& a, size_t head, int lane, float4 v) {
+    if (a.out) *reinterpret_cast<float4*>(a.out + head * 128 + 4 * lane) = v;
+    if (a.out_q) {
+        float am = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+        const float sc = quant_scale_i8(am);
+        const uint32_t q = (uint32_t)(quant_i8(v.x, sc) & 255) | ((uint32_t)(quant_i8(v.y, sc) & 255) << 8) |
+                           ((uint32_t)(quant_i8(v.z, sc) & 255) << 16) | ((uint32_t)(quant_i8(v.w, sc) & 255) << 24);
+        *reinterpret_cast<uint32_t*>(a.out_q + head * 128 + 4 * lane) = q;
+        if ((lane & 3) == 0) a.out_qs[head * 8 + (lane >> 2)] = sc;
+    }
+}
+// The same for one dimension per thread (16 consecutive lanes hold one block).
+__device__ __forceinline__ void emit_head1(const AttnArgs& a, size_t head, int d, float v) {
+    if (a.out) a.out[head * 128 + d] = v;
+    if (a.out_q) {
+        float am = fabsf(v);
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        const float sc = quant_scale_i8(am);
+        a.out_q[head * 128 + d] = (int8_t)quant_i8(v, sc);
+        if ((d & 15) == 0) a.out_qs[head * 8 + (d >> 4)] = sc;
+    }
+}
 
 // Partial record of one (sequence, head, split): 128 un-normalised outputs, then max and sum.
 constexpr int kPartStride = kHd + 2;
@@ -110,8 +142,7 @@ __device__ __forceinline__ void last_arriver_merge(const AttnArgs& a, int m, int
         }
         lsum = warp_sum(lsum);
         const float inv = 1.0f / (lsum + 1e-9f);
-        *reinterpret_cast<float4*>(a.out + head * kHd + 4 * lane) =
-            make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        emit_head4(a, head, lane, make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv));
     }
     if (t == 0) a.tickets[m * a.nkv + kvh] = 0;
 }
@@ -312,7 +343,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const 
         }
         const size_t head = (size_t)m * a.nqh + h0 + h;
         if (a.nsplit == 1) {
-            a.out[head * kHd + d] = os * (1.0f / (ls + 1e-9f));
+            emit_head1(a, head, d, os * (1.0f / (ls + 1e-9f)));
         } else {
             float* rec = a.part + (head * a.nsplit + split) * kPartStride;
             rec[d] = os;
@@ -402,14 +433,14 @@ size_t attn_scratch_bytes(int M, int nqh, int nkv, int ctx) {
 
 template <typename KVT>
 static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
-    if (!a.out || (!a.Q && !a.qkv) || !a.K || !a.V || a.nqh < 1 || a.nkv < 1 || a.nqh % a.nkv != 0 || a.M < 1 || a.max_seq < 1)
+    if ((!a.out && !a.out_q) || (!a.Q && !a.qkv) || !a.K || !a.V || a.nqh < 1 || a.nkv < 1 || a.nqh % a.nkv != 0 || a.M < 1 || a.max_seq < 1)
         return cudaErrorInvalidValue;
     const int gq = a.nqh / a.nkv;
     if (gq != 1 && gq != 2 && gq != 4 && gq != 8) return cudaErrorInvalidValue;
     if (ctx_hint < 1) ctx_hint = 1;
     if (ctx_hint > a.max_seq) ctx_hint = a.max_seq;
     const bool use_mma = sizeof(KVT) == 2 && (gq == 4 || gq == 8) && (g_attn_mma || a.qkv);  // binary16 cache with grouped heads
-    if (a.qkv && !use_mma) return cudaErrorInvalidValue;  // the fused form exists in the tensor-core kernel only
+    if ((a.qkv || a.out_q) && !use_mma) return cudaErrorInvalidValue;  // these forms exist in the tensor-core kernel only
     int nsplit = choose_splits(a.M * a.nkv, ctx_hint, 2 * sm_count(current_device()));
     if ((size_t)a.M * a.nkv * sizeof(unsigned int) > kTicketBytes) nsplit = 1;  // thousands of pairs fill the GPU unsplit
     a.split_len = (ctx_hint + nsplit - 1) / nsplit;
@@ -501,6 +532,26 @@ extern "C" int bw_attention_decode_f16kv_fused(float* output, const float* qkv, 
     if (head_dim != kHd || !d_seq_pos || !qkv || !q_norm_w || !k_norm_w) return cudaErrorInvalidValue;
     AttnArgs a{};
     a.out = output; a.Q = nullptr; a.K = K_cache; a.V = V_cache; a.d_seq_pos = d_seq_pos; a.per_seq = 1;
+    a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
+    a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
+    a.qkv = qkv; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.eps = eps; a.rope_base = rope_base;
+    return attn_launch<__half>(a, ctx_hint > 0 ? ctx_hint : max_seq_len, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_attention_decode_f16kv_fused_q8(float* output_or_null, int8_t* out_q8, float* out_scale,
+                                                  const float* qkv, const float* q_norm_w, const float* k_norm_w,
+                                                  uint16_t* K_cache, uint16_t* V_cache, const int* d_seq_pos,
+                                                  int ctx_hint, int num_q_heads, int num_kv_heads, int head_dim,
+                                                  int max_seq_len, int M, size_t kv_batch_elems, size_t kv_layer_elems,
+                                                  float eps, float rope_base, void* stream) {
+    if (head_dim != kHd || !d_seq_pos || !qkv || !q_norm_w || !k_norm_w || !out_q8 || !out_scale)
+        return cudaErrorInvalidValue;
+    if (num_kv_heads < 1 || (num_q_heads != 4 * num_kv_heads && num_q_heads != 8 * num_kv_heads))
+        return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(out_q8) & 3) != 0) return cudaErrorInvalidValue;
+    AttnArgs a{};
+    a.out = output_or_null; a.out_q = out_q8; a.out_qs = out_scale;
+    a.Q = nullptr; a.K = K_cache; a.V = V_cache; a.d_seq_pos = d_seq_pos; a.per_seq = 1;
     a.nqh = num_q_heads; a.nkv = num_kv_heads; a.max_seq = max_seq_len; a.M = M;
     a.kv_batch_elems = kv_batch_elems; a.kv_layer_elems = kv_layer_elems;
     a.qkv = qkv; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.eps = eps; a.rope_base = rope_base;

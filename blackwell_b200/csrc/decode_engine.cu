@@ -50,6 +50,8 @@ struct bw_decode {
     // state
     uint16_t *kc = nullptr, *vc = nullptr;
     float *x = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr, *logits = nullptr;
+    int8_t* attn_q = nullptr;   // attention result block-16 quantized by the attention kernel (int8 mode, fused form)
+    float* attn_qs = nullptr;
     int *tokens_in = nullptr, *sampled = nullptr, *pos = nullptr;
     int *prompt = nullptr, *prompt_len = nullptr, *gen = nullptr;
     int max_prompt = 0, max_new = 0;
@@ -199,7 +201,13 @@ int enqueue_step(bw_decode* d, cudaStream_t st) {
         const Layer& L = d->layers[l];
         const size_t off = (size_t)l * d->kv_layer;
         BW_TRY(gemv(d, L.qkv, d->qkv, nullptr, d->x, nullptr, 0, L.rn_in, L.qkv.N, st));
-        if (nq / nkv == 4 || nq / nkv == 8) {  // head norm + RoPE + KV write inside the tensor-core attention kernel
+        const bool fused = nq / nkv == 4 || nq / nkv == 8;
+        const bool q8 = fused && c.act_bits == 8;   // the attention kernel quantizes its result for the O projection
+        if (q8) {
+            BW_TRY(bw_attention_decode_f16kv_fused_q8(nullptr, d->attn_q, d->attn_qs, d->qkv, L.qn, L.kn, d->kc, d->vc,
+                                                      d->pos, c.max_seq, nq, nkv, 128, c.max_seq, M, d->kv_batch, off,
+                                                      c.eps, c.rope_base, st));
+        } else if (fused) {  // head norm + RoPE + KV write inside the tensor-core attention kernel
             BW_TRY(bw_attention_decode_f16kv_fused(d->attn, d->qkv, L.qn, L.kn, d->kc, d->vc, d->pos, c.max_seq, nq, nkv, 128,
                                                    c.max_seq, M, d->kv_batch, off, c.eps, c.rope_base, st));
         } else {
@@ -208,7 +216,10 @@ int enqueue_step(bw_decode* d, cudaStream_t st) {
             BW_TRY(bw_attention_decode_f16kv(d->attn, d->q, d->kc, d->vc, d->pos, c.max_seq, nq, nkv, 128, c.max_seq, M,
                                              d->kv_batch, off, st));
         }
-        BW_TRY(gemv(d, L.o, d->x, d->x, d->attn, nullptr, 0, nullptr, H, st));
+        if (q8)
+            BW_TRY(bw_gemv_w4a8_q8_decode(d->x, 0, d->x, d->attn_q, d->attn_qs, L.o.packed, L.o.sc16, L.o.K, H, M, st));
+        else
+            BW_TRY(gemv(d, L.o, d->x, d->x, d->attn, nullptr, 0, nullptr, H, st));
         BW_TRY(gemv(d, L.gu, d->gu, nullptr, d->x, nullptr, 0, L.rn_post, 2 * I, st));
         BW_TRY(gemv(d, L.down, d->x, d->x, d->gu, d->gu + I, 2 * (long)I, nullptr, H, st));
     }
@@ -229,6 +240,8 @@ int alloc_state(bw_decode* d) {
     BW_TRY(dev_alloc(d, &d->qkv, M * (size_t)(c.n_q_heads + 2 * c.n_kv_heads) * 128));
     BW_TRY(dev_alloc(d, &d->q, M * (size_t)c.n_q_heads * 128));
     BW_TRY(dev_alloc(d, &d->attn, M * (size_t)c.n_q_heads * 128));
+    BW_TRY(dev_alloc(d, &d->attn_q, M * (size_t)c.n_q_heads * 128));
+    BW_TRY(dev_alloc(d, &d->attn_qs, M * (size_t)c.n_q_heads * 8));
     BW_TRY(dev_alloc(d, &d->gu, M * 2 * (size_t)c.inter));
     BW_TRY(dev_alloc(d, &d->logits, M * (size_t)c.vocab));
     BW_TRY(dev_alloc(d, &d->tokens_in, M));

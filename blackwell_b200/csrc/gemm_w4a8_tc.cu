@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(256) prep_x_kernel(unsigned char* xb, const Ge
     reinterpret_cast<float*>(chunk + (size_t)b_chunk_bytes(Mpad))[b * Mpad + m] = s * kXScaleUp;
 }
 
-// The same quantize for the streaming kernels (3 to 16 sequences): plain int8 [M][K] and fp32 scales [M][K/16], the
+// The same quantize for the streaming kernels (2 to 16 sequences): plain int8 [M][K] and fp32 scales [M][K/16], the
 // layout of pre-quantized activations.  Without it every CTA of the GEMV quantizes all M x K activations itself
 // (RMSNorm or SwiGLU included), which at 8 sequences costs more than the weight stream of the per-layer matrices
 // (measured, 8B shape, 8 sequences: QKV 18.6 -> 10.0 us, gate+up 31.1 -> 22.6, down with SwiGLU 45.5 -> 18.4 without the

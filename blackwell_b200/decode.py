@@ -87,6 +87,8 @@ class DecodeEngine:
         self.qkv = torch.zeros((M, self.qkv_n), dtype=f32, device=dev)
         self.q = torch.zeros((M, self.nq * 128), dtype=f32, device=dev)
         self.attn = torch.zeros((M, self.nq * 128), dtype=f32, device=dev)
+        self.attn_q = torch.zeros((M, self.nq * 128), dtype=torch.int8, device=dev)      # the same, block-16 int8
+        self.attn_qs = torch.zeros((M, self.nq * 8), dtype=f32, device=dev)
         self.gu = torch.zeros((M, 2 * self.i_local), dtype=f32, device=dev)
         self.part = torch.zeros((M, H), dtype=f32, device=dev)
         self.logits = torch.zeros((M, self.v_local), dtype=f32, device=dev)
@@ -199,23 +201,29 @@ class DecodeEngine:
             off = l * self.kv_layer
             k.gemv_w4a8_decode(self.qkv, 0, None, self.x, None, 0, L["rn_in"], eps, L["qkv"][0], L["qkv"][1], H,
                                self.qkv_n, M)
-            if self.nq // self.nkv in (4, 8):   # head norm + RoPE + KV write inside the tensor-core attention kernel
-                k.attention_decode_f16kv_fused(self.attn, self.qkv, L["qn"], L["kn"], self.kc, self.vc, self.pos,
-                                               self.ctx_hint, self.nq, self.nkv, 128, self.max_seq, M, self.kv_batch,
-                                               off, eps, ROPE_BASE)
+            fused = self.nq // self.nkv in (4, 8)
+            if fused:   # head norm + RoPE + KV write inside the tensor-core attention kernel, which also quantizes its
+                # result for the O projection (the float copy is kept for inspection)
+                k.attention_decode_f16kv_fused_q8(self.attn, self.attn_q, self.attn_qs, self.qkv, L["qn"], L["kn"],
+                                                  self.kc, self.vc, self.pos, self.ctx_hint, self.nq, self.nkv, 128,
+                                                  self.max_seq, M, self.kv_batch, off, eps, ROPE_BASE)
             else:
                 k.qk_norm_rope_kv_f16(self.q, self.kc, self.vc, self.qkv, L["qn"], L["kn"], self.pos, self.nq,
                                       self.nkv, 128, self.max_seq, M, self.kv_batch, off, eps, ROPE_BASE)
                 k.attention_decode_f16kv(self.attn, self.q, self.kc, self.vc, self.pos, self.ctx_hint, self.nq,
                                          self.nkv, 128, self.max_seq, M, self.kv_batch, off)
+            def o_proj(y, res):
+                if fused:
+                    k.gemv_w4a8_q8_decode(y, 0, res, self.attn_q, self.attn_qs, L["o"][0], L["o"][1], self.nq * 128, H, M)
+                else:
+                    k.gemv_w4a8_decode(y, 0, res, self.attn, None, 0, None, 0.0, L["o"][0], L["o"][1], self.nq * 128,
+                                       H, M)
+
             if self.world == 1:
-                k.gemv_w4a8_decode(self.x, 0, self.x, self.attn, None, 0, None, 0.0, L["o"][0], L["o"][1],
-                                   self.nq * 128, H, M)
+                o_proj(self.x, self.x)
             else:
-                res = self.x if self.rank == 0 else None  # the residual enters the sum once
                 part = self._partial_target()
-                k.gemv_w4a8_decode(part, 0, res, self.attn, None, 0, None, 0.0, L["o"][0], L["o"][1],
-                                   self.nq * 128, H, M)
+                o_proj(part, self.x if self.rank == 0 else None)   # the residual enters the sum once
                 self._exchange(part)
             k.gemv_w4a8_decode(self.gu, 0, None, self.x, None, 0, L["rn_post"], eps, L["gu"][0], L["gu"][1], H,
                                2 * self.i_local, M)

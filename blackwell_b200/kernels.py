@@ -222,6 +222,12 @@ def gemv_w4a8_decode(y_out, y_stride, residual, x_f32, up, x_stride, norm_weight
         C.c_float(eps), _p(W_packed), _p(W_scale_f16), K, N, M, _s(stream)))
 
 
+def gemv_w4a8_q8_decode(y_out, y_stride, residual, x_q, x_scale, W_packed, W_scale_f16, K, N, M, stream=None):
+    _chk("gemv_w4a8_q8_decode", _L.bw_gemv_w4a8_q8_decode(
+        _p(y_out), C.c_long(y_stride), _p(residual), _p(x_q), _p(x_scale), _p(W_packed), _p(W_scale_f16), K, N, M,
+        _s(stream)))
+
+
 def qk_norm_rope_kv_f16(q_out, k_cache, v_cache, qkv, q_norm_w, k_norm_w, d_seq_pos, num_q_heads, num_kv_heads,
                         head_dim, max_seq_len, M, kv_batch_elems, kv_layer_elems, eps, rope_base, stream=None):
     _chk("qk_norm_rope_kv_f16", _L.bw_qk_norm_rope_kv_f16(
@@ -248,6 +254,15 @@ def sample_argmax_candidates(logits, row_stride, vocab, M, index_offset, cand_ou
 def sample_argmax_merge(cand_all_pairs, world, M, out_ids, seq_pos_to_advance=None, pos_limit=0, stream=None):
     _chk("sample_argmax_merge", _L.bw_sample_argmax_merge(_p(cand_all_pairs), world, M, _p(out_ids),
                                                           _p(seq_pos_to_advance), int(pos_limit), _s(stream)))
+
+
+def attention_decode_f16kv_fused_q8(output, out_q8, out_scale, qkv, q_norm_w, k_norm_w, k_cache, v_cache, d_seq_pos,
+                                    ctx_hint, num_q_heads, num_kv_heads, head_dim, max_seq_len, M, kv_batch_elems,
+                                    kv_layer_elems, eps, rope_base, stream=None):
+    _chk("attention_decode_f16kv_fused_q8", _L.bw_attention_decode_f16kv_fused_q8(
+        _p(output), _p(out_q8), _p(out_scale), _p(qkv), _p(q_norm_w), _p(k_norm_w), _p(k_cache), _p(v_cache),
+        _p(d_seq_pos), ctx_hint, num_q_heads, num_kv_heads, head_dim, max_seq_len, M, C.c_size_t(kv_batch_elems),
+        C.c_size_t(kv_layer_elems), C.c_float(eps), C.c_float(rope_base), _s(stream)))
 
 
 def attention_decode_f16kv_fused(output, qkv, q_norm_w, k_norm_w, k_cache, v_cache, d_seq_pos, ctx_hint, num_q_heads,

@@ -79,6 +79,12 @@ int bw_gemv_w4a8_decode(float* y_out, long y_stride, const float* residual_or_nu
                         const float* up_or_null, long x_stride, const float* norm_weight_or_null, float eps,
                         const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N, int M, void* stream);
 
+/* bw_gemv_w4a8 with the output stride and residual epilogue of bw_gemv_w4a8_decode: pre-quantized int8 activations
+ * [M][K] and scales [M][K/16] (from bw_quantize_int8*, or from bw_attention_decode_f16kv_fused_q8). */
+int bw_gemv_w4a8_q8_decode(float* y_out, long y_stride, const float* residual_or_null, const int8_t* x_q,
+                           const float* x_scale, const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N,
+                           int M, void* stream);
+
 /* Reference-format (W4A4, fp32 scales) GEMV with fused prologues: the int4
  * quantize rule of quantize_int4 (kernels.h:800-816) applied to x, to
  * rmsnorm(x) (norm_weight != NULL) or to silu(gate)*up (up != NULL).  M <= 8 (fp32 scales stay on the dp4a
@@ -215,6 +221,16 @@ int bw_attention_decode_f16kv_fused(float* output, const float* qkv, const float
                                     int num_q_heads, int num_kv_heads, int head_dim, int max_seq_len, int M,
                                     size_t kv_batch_elems, size_t kv_layer_elems, float eps, float rope_base,
                                     void* stream);
+
+/* The same launch with the result also (or only: output_or_null == NULL) block-16 quantized to int8 by the rule of
+ * bw_quantize_int8 -- out_q8 i8 [M][num_q_heads][128], out_scale f32 [M][num_q_heads][8] -- which is what the O
+ * projection takes as pre-quantized activations (bw_gemv_w4a8_q8_decode), so that no CTA of that GEMV has to
+ * quantize them.  Same bits as quantizing the float result.  No counterpart in the reference. */
+int bw_attention_decode_f16kv_fused_q8(float* output_or_null, int8_t* out_q8, float* out_scale, const float* qkv,
+                                       const float* q_norm_w, const float* k_norm_w, uint16_t* K_cache,
+                                       uint16_t* V_cache, const int* d_seq_pos, int ctx_hint, int num_q_heads,
+                                       int num_kv_heads, int head_dim, int max_seq_len, int M, size_t kv_batch_elems,
+                                       size_t kv_layer_elems, float eps, float rope_base, void* stream);
 
 /* Attention for callers that must not allocate.  No counterpart in the reference: it exists for hosts
  * that cannot reach the CUDA allocator once they are serving -- a process that has given all device memory
@@ -360,7 +376,8 @@ int bw_reserve_scratch(size_t gemv_bytes, size_t attention_bytes);
  * mma.sync kernel (0 = off; 1 = skip its arithmetic, 2 = skip its copies: results are then meaningless), key 18 =
  * its packed form for up to 4 sequences on (1, default) / off (0), key 19 = timing experiments on the tcgen05
  * kernel (0 = off; bits: 1 no epilogue arithmetic, 2 no unpack, 4 no weight loads, 8 no MMAs, 16 / 32 no activation /
- * activation-scale copies, 64 no weight-scale loads: results are then meaningless). */
+ * activation-scale copies, 64 no weight-scale loads: results are then meaningless), key 20 = smallest batch whose
+ * float activations are quantized once by a separate kernel before a streaming GEMV (0 = default 2). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);

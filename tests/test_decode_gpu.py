@@ -204,6 +204,28 @@ def test_fused_norm_rope_kv_attention_equals_the_two_launches(cuda, nq, nkv):
     torch.cuda.synchronize()
     assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
     assert torch.equal(out1, out2)
+    # the quantized second output: the bits of bw_quantize_int8 applied to the float result, with split merge (hint
+    # 300 of up to 700 positions) and without (a hint of 8 positions gives one open-ended split)
+    for h in (hint, 8):
+        kc3, vc3 = kc1.clone(), vc1.clone()
+        out3 = torch.full_like(out1, float("nan"))
+        oq = torch.zeros((M, nq * 128), dtype=torch.int8, device="cuda")
+        os_ = torch.zeros((M, nq * 8), dtype=torch.float32, device="cuda")
+        k.attention_decode_f16kv_fused_q8(out3, oq, os_, qkv, qn, kn, kc3, vc3, pos, h, nq, nkv,
+                                          128, max_seq, M, layers * kv_layer, layer * kv_layer, 1e-6, 1e6)
+        torch.cuda.synchronize()
+        ref_q, ref_s = oracle.quantize_int8(out3.cpu().numpy())
+        assert np.array_equal(oq.cpu().numpy(), ref_q) and np.array_equal(os_.cpu().numpy(), ref_s)
+        if h == hint:
+            assert torch.equal(out3, out2)
+        # the O projection on the quantized operand equals the one that quantizes the float result itself
+        W, sc16, _ = synth.int4_weights(256, nq * 128, seed=445)
+        Wd, sd = to_dev(W), to_dev(sc16.view(np.uint16))
+        res = to_dev(synth.activations_f16(M, 256, 446).astype(np.float32))
+        y1, y2 = res.clone(), res.clone()
+        k.gemv_w4a8_decode(y1, 0, y1, out3, None, 0, None, 0.0, Wd, sd, nq * 128, 256, M)
+        k.gemv_w4a8_q8_decode(y2, 0, y2, oq, os_, Wd, sd, nq * 128, 256, M)
+        assert torch.equal(y1, y2)
     assert k.device_status() == 0
 
 
