@@ -68,14 +68,13 @@ __global__ void __launch_bounds__(256) prep_x_kernel(unsigned char* xb, const Ge
 // layout of pre-quantized activations.  Without it every CTA of the GEMV quantizes all M x K activations itself
 // (RMSNorm or SwiGLU included), which at 8 sequences costs more than the weight stream of the per-layer matrices
 // (measured, 8B shape, 8 sequences: QKV 18.6 -> 10.0 us, gate+up 31.1 -> 22.6, down with SwiGLU 45.5 -> 18.4 without the
-// prologue).  Grid (ceil(K / 16 / 256), M), 256 threads; starts early under programmatic dependent launch.
+// prologue).  Grid (ceil(K / 1024), M), 256 threads; starts early under programmatic dependent launch.
 __global__ void __launch_bounds__(256) prep_plain_kernel(int8_t* xq, float* xs, const GemvArgs a, int M) {
     __shared__ float part[8];
     __shared__ float rstd_s;
     pdl_trigger();
     pdl_wait();   // the activations come from the kernel before
     const int m = blockIdx.y, t = threadIdx.x;
-    const int nkb = a.K / 16;
     float rstd = 1.f;
     if (a.xkind == kXFloatNorm) {
         float ss = 0.f;
@@ -95,14 +94,51 @@ __global__ void __launch_bounds__(256) prep_plain_kernel(int8_t* xq, float* xs, 
         __syncthreads();
         rstd = rstd_s;
     }
-    const int kb = blockIdx.x * 256 + t;
-    if (kb >= nkb) return;
-    uint32_t e[2], o[2];
-    float s;
-    make_xblock(a, m, kb, rstd, e, o, s);   // even-k / odd-k bytes and scale / 16
-    *reinterpret_cast<uint4*>(xq + (size_t)m * a.K + 16 * (size_t)kb) =
-        make_uint4(prmt(e[0], o[0], 0x5140), prmt(e[0], o[0], 0x7362), prmt(e[1], o[1], 0x5140), prmt(e[1], o[1], 0x7362));
-    xs[(size_t)m * nkb + kb] = s * 16.0f;
+    // Four consecutive elements per thread, four threads per k-block (K % 32 == 0, so a block's threads are valid or
+    // not together); the element arithmetic is that of make_xblock, the rounding that of quantize_block.
+    const int e0 = (blockIdx.x * 256 + t) * 4;
+    const bool valid = e0 < a.K;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (valid) {
+        if (a.xkind == kXHalf) {
+            const uint2 u = __ldg(reinterpret_cast<const uint2*>(static_cast<const __half*>(a.x) + (size_t)m * a.x_stride + e0));
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+            v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y;
+        } else {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * a.x_stride + e0));
+            v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+            if (a.xkind == kXFloatNorm) {
+                const float4 gw = __ldg(reinterpret_cast<const float4*>(a.norm_w + e0));
+                v[0] = v[0] * gw.x * rstd; v[1] = v[1] * gw.y * rstd; v[2] = v[2] * gw.z * rstd; v[3] = v[3] * gw.w * rstd;
+            } else if (a.xkind == kXSwiglu) {
+                const float4 u = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(a.x2) + (size_t)m * a.x_stride + e0));
+                v[0] = silu_mul(v[0], u.x); v[1] = silu_mul(v[1], u.y); v[2] = silu_mul(v[2], u.z); v[3] = silu_mul(v[3], u.w);
+            }
+        }
+    }
+    float am = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+    if (!valid) return;
+    const float sc = quant_scale_i8(am);
+    const float rcp = 1.0f / sc;
+    uint32_t qb[4];
+    bool exact_needed = !(am < 3.0e38f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float r = v[i] * rcp;
+        const float mg = r + kMagicFloat;
+        const float ri = mg - kMagicFloat;
+        exact_needed |= !(fabsf(fabsf(r - ri) - 0.5f) > 3e-5f);
+        qb[i] = __float_as_uint(mg);
+    }
+    if (exact_needed) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qb[i] = (uint32_t)quant_i8(v[i], sc);
+    }
+    *reinterpret_cast<uint32_t*>(xq + (size_t)m * a.K + e0) = prmt(prmt(qb[0], qb[1], 0x0040), prmt(qb[2], qb[3], 0x0040), 0x5410);
+    if ((t & 3) == 0) xs[(size_t)m * (a.K / 16) + (e0 >> 4)] = sc;
 }
 
 // ----------------------------------------------------------------------------------------------------------
@@ -574,7 +610,7 @@ cudaError_t prepare_plain(const GemvArgs& a, int M, cudaStream_t st, const int8_
     if (e != cudaSuccess) return e;
     int8_t* xq = reinterpret_cast<int8_t*>(scratch + kTicketBytes);
     float* xs = reinterpret_cast<float*>(scratch + kTicketBytes + q_bytes);
-    const dim3 grid((a.K / 16 + 255) / 256, M);
+    const dim3 grid((a.K + 1023) / 1024, M);
     e = launch_pdl(prep_plain_kernel, grid, dim3(256), 0, st, xq, xs, a, M);
     count_launch(1);
     if (e != cudaSuccess) return e;

@@ -132,7 +132,7 @@ static std::atomic<int> g_tune_stages{0}, g_tune_ctas{0}, g_tune_force_plain{0},
 static std::atomic<int> g_tune_shrink_ring{1};
 static std::atomic<int> g_tune_mma_mode{0};
 static std::atomic<int> g_tune_mma_pack{1};
-static std::atomic<int> g_tune_prep_min{0};
+static std::atomic<int> g_tune_prep_min{0}, g_tune_prep_min_swiglu{0};
 #ifdef BW_GEMV_TIMELINE
 static unsigned long long* g_timeline_ptr = nullptr;
 extern "C" void bw_debug_set_timeline(void* dev_ptr) { g_timeline_ptr = static_cast<unsigned long long*>(dev_ptr); }
@@ -449,7 +449,8 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
     // its activations quantized once by a small kernel instead of once per CTA; the GEMV then runs on the result as on
     // any pre-quantized operand (same quantize code, same bits).
     const int prep_min = g_tune_prep_min.load() > 0 ? g_tune_prep_min.load() : 2;   // measured: a loss at 1
-    if (!use_tc && M >= prep_min && a.K % 32 == 0 &&
+    const int prep_min_sw = g_tune_prep_min_swiglu.load() > 0 ? g_tune_prep_min_swiglu.load() : 1;   // SwiGLU: a gain at 1 too
+    if (!use_tc && M >= (a.xkind == kXSwiglu ? prep_min_sw : prep_min) && a.K % 32 == 0 &&
         (a.xkind == kXHalf || a.xkind == kXFloat || a.xkind == kXFloatNorm || a.xkind == kXSwiglu)) {
         const int8_t* xq = nullptr;
         const float* xs = nullptr;
@@ -687,6 +688,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 18: g_tune_mma_pack = value; return 0;
         case 19: tc::set_ablate(value); return 0;
         case 20: g_tune_prep_min = value; return 0;
+        case 21: g_tune_prep_min_swiglu = value; return 0;
         default: return cudaErrorInvalidValue;
     }
 }

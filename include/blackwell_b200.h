@@ -377,7 +377,8 @@ int bw_reserve_scratch(size_t gemv_bytes, size_t attention_bytes);
  * its packed form for up to 4 sequences on (1, default) / off (0), key 19 = timing experiments on the tcgen05
  * kernel (0 = off; bits: 1 no epilogue arithmetic, 2 no unpack, 4 no weight loads, 8 no MMAs, 16 / 32 no activation /
  * activation-scale copies, 64 no weight-scale loads: results are then meaningless), key 20 = smallest batch whose
- * float activations are quantized once by a separate kernel before a streaming GEMV (0 = default 2). */
+ * float activations are quantized once by a separate kernel before a streaming GEMV (0 = default 2), key 21 = the
+ * same for the SwiGLU prologue (0 = default 1). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);
