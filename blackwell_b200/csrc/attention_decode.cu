@@ -128,15 +128,22 @@ __device__ __forceinline__ void last_arriver_merge(const AttnArgs& a, int m, int
                 }
             }
             const int cnt = min(32, a.nsplit - s0);
-#pragma unroll 4
-            for (int j = 0; j < cnt; ++j) {
-                const float cj = __shfl_sync(0xffffffffu, c, j);
-                if (cj != 0.f) {
+            // Sixteen records in flight per lane: every load is an L2 round trip, and with four at a time the merge of
+            // ~32 splits took longer than streaming the cache.  Records of empty splits hold zeros and get weight 0.
+            for (int j0 = 0; j0 < cnt; j0 += 16) {
+                float2 r0[16], r1[16];
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) {
+                    const int j = min(j0 + jj, cnt - 1);   // clamped reads are weighted 0 below
                     const float* rec = base + (size_t)(s0 + j) * kPartStride + 4 * lane;
-                    const float2 r0 = __ldcg(reinterpret_cast<const float2*>(rec));
-                    const float2 r1 = __ldcg(reinterpret_cast<const float2*>(rec + 2));
-                    acc.x = fmaf(cj, r0.x, acc.x); acc.y = fmaf(cj, r0.y, acc.y);
-                    acc.z = fmaf(cj, r1.x, acc.z); acc.w = fmaf(cj, r1.y, acc.w);
+                    r0[jj] = __ldcg(reinterpret_cast<const float2*>(rec));
+                    r1[jj] = __ldcg(reinterpret_cast<const float2*>(rec + 2));
+                }
+#pragma unroll
+                for (int jj = 0; jj < 16; ++jj) {
+                    const float cj = j0 + jj < cnt ? __shfl_sync(0xffffffffu, c, (j0 + jj) & 31) : 0.f;
+                    acc.x = fmaf(cj, r0[jj].x, acc.x); acc.y = fmaf(cj, r0[jj].y, acc.y);
+                    acc.z = fmaf(cj, r1[jj].x, acc.z); acc.w = fmaf(cj, r1[jj].y, acc.w);
                 }
             }
         }
@@ -398,26 +405,41 @@ cudaError_t attn_reserve_scratch(size_t bytes) {
     return bytes ? g_attn_scratch.get(bytes, (size_t)4 << 20, nullptr, &p) : cudaSuccess;
 }
 
-// Number of context splits: the grid is (sequence, kv head) pairs x splits, `slots` CTAs are resident at a time, and a
-// last wave that is mostly empty costs as much as a full one.  Takes the smallest split count (at least ~2 CTAs per SM, at least
-// 64 positions per split, at most 64 splits) whose last wave is at least 90 % full, else the fullest one.
-static int choose_splits(int pairs, int ctx, int slots) {
-    int max_split = (ctx + 63) / 64;
-    if (max_split > 64) max_split = 64;
-    if (max_split < 1) max_split = 1;
-    int lo = (slots + pairs - 1) / pairs;
-    if (lo > max_split) lo = max_split;
-    if (lo < 1) lo = 1;
-    int best = lo;
-    double best_eff = 0.0;
-    for (int n = lo; n <= max_split && n <= lo + 16; ++n) {
-        const long ctas = (long)pairs * n;
-        const long waves = (ctas + slots - 1) / slots;
-        const double eff = (double)ctas / (double)(waves * slots);
-        if (eff >= 0.9) return n;
-        if (eff > best_eff) { best_eff = eff; best = n; }
+// Number of context splits; the grid is (sequence, kv head) pairs x splits.  Measured on a B200 (32 / 8 heads, binary16
+// cache; a launch in a chain of its own kind and inside the 8B-shape decode step): the fastest grid is ONE wave of about
+// two CTAs per SM -- an SM streams ~50 GB/s, so fewer CTAs cannot pull the bandwidth (8 sequences x 8 kv heads at 2048
+// positions: unsplit 40.6 us, 4 splits 20.3 us), while a second wave or splits shorter than ~224 positions cost more in
+// partial records, arrival counters and merges than they gain (the same case with 9 splits: 28.4 us; batch 1 at ctx
+// 2048 inside the decode step: 1.90 ms per step with 33 splits of 62 positions, 1.84 ms with 9 of 228).  So: the largest
+// split count whose grid still fits one wave, at least 224 positions per split, at most 64 splits.
+// `bw_set_tuning(22, pct)` selects the earlier rule instead (smallest count whose last wave of pct % x SMs slots is 90 %
+// full, 64 positions per split at least).
+static int g_attn_slots_pct = 0;
+void set_attn_slots_pct(int v) { g_attn_slots_pct = v > 0 ? v : 0; }
+static int choose_splits(int pairs, int ctx, int sms) {
+    if (g_attn_slots_pct > 0) {
+        const int slots = g_attn_slots_pct * sms / 100 > 0 ? g_attn_slots_pct * sms / 100 : 1;
+        int max_split = (ctx + 63) / 64;
+        if (max_split > 64) max_split = 64;
+        int lo = (slots + pairs - 1) / pairs;
+        if (lo > max_split) lo = max_split;
+        if (lo < 1) lo = 1;
+        int best = lo;
+        double best_eff = 0.0;
+        for (int n = lo; n <= max_split && n <= lo + 16; ++n) {
+            const long ctas = (long)pairs * n;
+            const long waves = (ctas + slots - 1) / slots;
+            const double eff = (double)ctas / (double)(waves * slots);
+            if (eff >= 0.9) return n;
+            if (eff > best_eff) { best_eff = eff; best = n; }
+        }
+        return best;
     }
-    return best;
+    int n = 2 * sms / pairs;                        // one wave of two CTAs per SM
+    const int by_len = ctx / 224;                   // at least 224 positions per split
+    if (n > by_len) n = by_len;
+    if (n > 64) n = 64;
+    return n < 1 ? 1 : n;
 }
 
 // The arrival counters live in a region of fixed size at the front of the scratch block that nothing else ever
@@ -441,7 +463,7 @@ static cudaError_t attn_launch(AttnArgs a, int ctx_hint, cudaStream_t st) {
     if (ctx_hint > a.max_seq) ctx_hint = a.max_seq;
     const bool use_mma = sizeof(KVT) == 2 && (gq == 4 || gq == 8) && (g_attn_mma || a.qkv);  // binary16 cache with grouped heads
     if ((a.qkv || a.out_q) && !use_mma) return cudaErrorInvalidValue;  // these forms exist in the tensor-core kernel only
-    int nsplit = choose_splits(a.M * a.nkv, ctx_hint, 2 * sm_count(current_device()));
+    int nsplit = choose_splits(a.M * a.nkv, ctx_hint, sm_count(current_device()));
     if ((size_t)a.M * a.nkv * sizeof(unsigned int) > kTicketBytes) nsplit = 1;  // thousands of pairs fill the GPU unsplit
     a.split_len = (ctx_hint + nsplit - 1) / nsplit;
     a.split_len = (a.split_len + kPosPerStep - 1) / kPosPerStep * kPosPerStep;

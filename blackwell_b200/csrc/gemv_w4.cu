@@ -16,6 +16,7 @@
 
 namespace bw {
 
+void set_attn_slots_pct(int v);
 void set_attn_mma(int v);  // attention_decode.cu
 cudaError_t attn_reserve_scratch(size_t bytes);
 size_t attn_scratch_bytes(int M, int nqh, int nkv, int ctx);
@@ -689,6 +690,7 @@ extern "C" int bw_set_tuning(int key, int value) {
         case 19: tc::set_ablate(value); return 0;
         case 20: g_tune_prep_min = value; return 0;
         case 21: g_tune_prep_min_swiglu = value; return 0;
+        case 22: set_attn_slots_pct(value); return 0;
         default: return cudaErrorInvalidValue;
     }
 }

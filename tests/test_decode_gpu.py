@@ -182,11 +182,11 @@ def test_fused_norm_rope_kv_attention_equals_the_two_launches(cuda, nq, nkv):
 
     from blackwell_b200 import kernels as k
 
-    M, max_seq, hint = 6, 700, 300
+    M, max_seq, hint = 6, 1400, 800   # three splits of 268 positions
     g = synth.rng(440 + nq + nkv)
     qkv = to_dev(g.normal(size=(M, (nq + 2 * nkv) * 128)).astype(np.float32))
     qn, kn = to_dev(synth.norm_weight(128, 441)), to_dev(synth.norm_weight(128, 442))
-    pos = to_dev(np.array([0, 63, 64, 299, 650, 700], np.int32))
+    pos = to_dev(np.array([0, 267, 268, 799, 1300, 1400], np.int32))
     layers, layer = 2, 1
     kv_layer = nkv * max_seq * 128
     base = synth.kv_cache_f16((M, layers * kv_layer), 443)
@@ -205,7 +205,7 @@ def test_fused_norm_rope_kv_attention_equals_the_two_launches(cuda, nq, nkv):
     assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
     assert torch.equal(out1, out2)
     # the quantized second output: the bits of bw_quantize_int8 applied to the float result, with split merge (hint
-    # 300 of up to 700 positions) and without (a hint of 8 positions gives one open-ended split)
+    # 800 of up to 1400 positions) and without (a hint of 8 positions gives one open-ended split)
     for h in (hint, 8):
         kc3, vc3 = kc1.clone(), vc1.clone()
         out3 = torch.full_like(out1, float("nan"))

@@ -248,6 +248,16 @@ def test_attention_arrival_counters_survive_a_smaller_call_before_a_larger_one(k
     import torch
 
     hd, max_seq = 128, 640
+    k.set_tuning(22, 200)   # the split rule that aims at two CTAs per SM: these small contexts are then split
+    try:
+        _counter_cases(k, hd, max_seq)
+    finally:
+        k.set_tuning(22, 0)
+
+
+def _counter_cases(k, hd, max_seq):
+    import torch
+
     for M, nqh, nkv, seed in [(2, 32, 8, 240), (24, 32, 8, 241), (3, 16, 4, 242), (40, 8, 8, 243)]:
         g = synth.rng(seed)
         Q = g.normal(size=(M, nqh * hd)).astype(np.float32)
@@ -267,12 +277,12 @@ def test_attention_f16_cache_context_longer_than_the_hint(k, nqh, nkv):
     times) must still attend to every position (tensor-core kernel: 4 heads per kv head; scalar kernel: 2)."""
     import torch
 
-    M, hd, max_seq, hint = 3, 128, 1024, 200
+    M, hd, max_seq, hint = 3, 128, 2048, 800   # three splits of 268 positions
     g = synth.rng(230)
     Q = g.normal(size=(M, nqh * hd)).astype(np.float32)
     Kc = synth.kv_cache_f16((M, nkv, max_seq, hd), 231)
     Vc = synth.kv_cache_f16((M, nkv, max_seq, hd), 232)
-    pos = np.array([150, 777, 1023], np.int32)
+    pos = np.array([150, 1500, 2047], np.int32)
     out = torch.empty((M, nqh * hd), dtype=torch.float32, device="cuda")
     k.attention_decode_f16kv(out, to_dev(Q), to_dev(Kc.view(np.uint16)), to_dev(Vc.view(np.uint16)), to_dev(pos),
                              hint, nqh, nkv, hd, max_seq, M, nkv * max_seq * hd, 0)
