@@ -110,41 +110,46 @@ __device__ __forceinline__ void last_arriver_merge(const AttnArgs& a, int m, int
     for (int h = warp; h < GQ; h += kAttnWarps) {
         const size_t head = (size_t)m * a.nqh + h0 + h;
         const float* base = a.part + head * a.nsplit * kPartStride;
-        float mloc = -FLT_MAX;
-        for (int s = lane; s < a.nsplit; s += 32)
-            if (__ldcg(base + (size_t)s * kPartStride + kHd + 1) > 0.f)
-                mloc = fmaxf(mloc, __ldcg(base + (size_t)s * kPartStride + kHd));
-        const float mall = warp_max(mloc);
-        float lsum = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < a.nsplit; s0 += 32) {
-            const int s = s0 + lane;
-            float c = 0.f;
-            if (s < a.nsplit) {
-                const float ls = __ldcg(base + (size_t)s * kPartStride + kHd + 1);
-                if (ls > 0.f) {
-                    c = __expf(__ldcg(base + (size_t)s * kPartStride + kHd) - mall);
-                    lsum = fmaf(ls, c, lsum);
-                }
+        // Every load is an L2 round trip, so all of them are requested up front: the (max, sum) pairs of up to 64 splits
+        // (two per lane) and the first sixteen records; with four records at a time and the pairs read twice, the merge
+        // of ~32 splits took longer than streaming the cache.  Records of empty splits hold zeros and get weight 0.
+        float ms[2], ls[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int sp = min(lane + 32 * r, a.nsplit - 1);
+            ms[r] = __ldcg(base + (size_t)sp * kPartStride + kHd);
+            ls[r] = lane + 32 * r < a.nsplit ? __ldcg(base + (size_t)sp * kPartStride + kHd + 1) : 0.f;
+        }
+        float2 r0[16], r1[16];
+        auto load_batch = [&](int j0) {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+                const float* rec = base + (size_t)min(j0 + jj, a.nsplit - 1) * kPartStride + 4 * lane;  // clamped: weight 0
+                r0[jj] = __ldcg(reinterpret_cast<const float2*>(rec));
+                r1[jj] = __ldcg(reinterpret_cast<const float2*>(rec + 2));
             }
-            const int cnt = min(32, a.nsplit - s0);
-            // Sixteen records in flight per lane: every load is an L2 round trip, and with four at a time the merge of
-            // ~32 splits took longer than streaming the cache.  Records of empty splits hold zeros and get weight 0.
-            for (int j0 = 0; j0 < cnt; j0 += 16) {
-                float2 r0[16], r1[16];
+        };
+        load_batch(0);
+        float mloc = -FLT_MAX;
 #pragma unroll
-                for (int jj = 0; jj < 16; ++jj) {
-                    const int j = min(j0 + jj, cnt - 1);   // clamped reads are weighted 0 below
-                    const float* rec = base + (size_t)(s0 + j) * kPartStride + 4 * lane;
-                    r0[jj] = __ldcg(reinterpret_cast<const float2*>(rec));
-                    r1[jj] = __ldcg(reinterpret_cast<const float2*>(rec + 2));
-                }
+        for (int r = 0; r < 2; ++r)
+            if (ls[r] > 0.f) mloc = fmaxf(mloc, ms[r]);
+        const float mall = warp_max(mloc);
+        float c[2], lsum = 0.f;
 #pragma unroll
-                for (int jj = 0; jj < 16; ++jj) {
-                    const float cj = j0 + jj < cnt ? __shfl_sync(0xffffffffu, c, (j0 + jj) & 31) : 0.f;
-                    acc.x = fmaf(cj, r0[jj].x, acc.x); acc.y = fmaf(cj, r0[jj].y, acc.y);
-                    acc.z = fmaf(cj, r1[jj].x, acc.z); acc.w = fmaf(cj, r1[jj].y, acc.w);
-                }
+        for (int r = 0; r < 2; ++r) {
+            c[r] = ls[r] > 0.f ? __expf(ms[r] - mall) : 0.f;
+            lsum = fmaf(ls[r], c[r], lsum);
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j0 = 0; j0 < a.nsplit; j0 += 16) {
+            if (j0 > 0) load_batch(j0);
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+                const int j = j0 + jj;   // warp-uniform
+                const float cj = j < a.nsplit ? __shfl_sync(0xffffffffu, j < 32 ? c[0] : c[1], j & 31) : 0.f;
+                acc.x = fmaf(cj, r0[jj].x, acc.x); acc.y = fmaf(cj, r0[jj].y, acc.y);
+                acc.z = fmaf(cj, r1[jj].x, acc.z); acc.w = fmaf(cj, r1[jj].y, acc.w);
             }
         }
         lsum = warp_sum(lsum);
@@ -276,21 +281,27 @@ template <int GQ>
 __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const AttnArgs a) {
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    pdl_trigger();
-    pdl_wait();
-    const int seq_pos = a.d_seq_pos ? a.d_seq_pos[a.per_seq ? m : 0] : a.seq_pos;
-    const int npos = min(seq_pos + 1, a.max_seq);
+    extern __shared__ __align__(128) unsigned char attn_dsm[];   // 4 warps x (K, V) x 2 buffers x 4 KB
     const int p0 = split * a.split_len;
-    // The last split runs to the sequence's own end: the split length is sized from a hint of the context, and a
-    // sequence that has grown past the hint must still see all its positions.
-    const int p1 = split == a.nsplit - 1 ? npos : min(npos, p0 + a.split_len);
     const __half* Kb = static_cast<const __half*>(a.K) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
                        (size_t)kvh * a.max_seq * kHd;
     const __half* Vb = static_cast<const __half*>(a.V) + (size_t)m * a.kv_batch_elems + a.kv_layer_elems +
                        (size_t)kvh * a.max_seq * kHd;
+    pdl_trigger();
+    // Fused form: the cache rows below this step's position were written by earlier steps, so every warp requests its
+    // first tile before waiting for the kernel before (whose QKV output and position this kernel needs): the tile's
+    // DRAM latency then overlaps that wait and the query prologue.  Which rows are usable is decided after the wait.
+    const bool early = a.qkv != nullptr && warp * amma::kTile < a.split_len && p0 + warp * amma::kTile < a.max_seq;
+    if (early)
+        amma::issue_tile(Kb, Vb, smem_u32(attn_dsm + warp * amma::kWarpSmem), 0, p0 + warp * amma::kTile, a.max_seq - 1);
+    pdl_wait();
+    const int seq_pos = a.d_seq_pos ? a.d_seq_pos[a.per_seq ? m : 0] : a.seq_pos;
+    const int npos = min(seq_pos + 1, a.max_seq);
+    // The last split runs to the sequence's own end: the split length is sized from a hint of the context, and a
+    // sequence that has grown past the hint must still see all its positions.
+    const int p1 = split == a.nsplit - 1 ? npos : min(npos, p0 + a.split_len);
     const int h0 = kvh * GQ;
 
-    extern __shared__ __align__(128) unsigned char attn_dsm[];   // 4 warps x (K, V) x 2 buffers x 4 KB
     __shared__ __align__(16) float s_q[GQ][kHd];
     __shared__ float s_m[kAttnWarps][GQ], s_l[kAttnWarps][GQ];
     __shared__ int s_last;
@@ -324,8 +335,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_decode_mma_kernel(const 
     __syncthreads();
 
     float m_run, l_run, o[32];
+    // rows that were final when the early tile was requested: all below this step's position (and inside the split)
     amma::warp_stream<GQ>(Kb, Vb, &s_q[0][0], a.scale, p0, p1, warp, kAttnWarps, attn_dsm + warp * amma::kWarpSmem,
-                          m_run, l_run, o);
+                          m_run, l_run, o, early, min(p1, seq_pos));
     {
         const int g = lane >> 2, tq = lane & 3;
         if (g < GQ) {

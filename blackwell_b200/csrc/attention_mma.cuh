@@ -56,13 +56,30 @@ constexpr int kWarpSmem = 4 * kTileBytes;   // K and V, two buffers each
 // byte offset of 16-byte chunk c of row r inside a tile (chunks XOR-swizzled by the row)
 __device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4)); }
 
+// One 16-position K/V tile of a warp into buffer `buf` of its staging area: rows past `last_row` are clamped to it
+// (the caller masks them, and a clamped row is real data where memory past the sequence's end may hold anything).
+__device__ __forceinline__ void issue_tile(const __half* Kb, const __half* Vb, uint32_t sbase, int buf, int tpos,
+                                           int last_row) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = i * 32 + lane;          // 256 chunks per tile
+        const int r = idx >> 4, c = idx & 15;
+        const int pos = min(tpos + r, last_row);
+        cp_async16(sbase + buf * 2 * kTileBytes + tile_off(r, c), Kb + (size_t)pos * 128 + c * 8);
+        cp_async16(sbase + buf * 2 * kTileBytes + kTileBytes + tile_off(r, c), Vb + (size_t)pos * 128 + c * 8);
+    }
+    cp_async_commit();
+}
+
 // Streams the positions [p0, p1) of one (sequence, kv head) through one warp: returns, for head g = lane / 4, the
 // running maximum, this thread's share of the softmax sum and the un-normalised outputs of dimensions
 // 8 * j + 2 * (lane % 4) + {0, 1}, j = 0..15, in o[2 * j + {0, 1}].
 template <int GQ>
 __device__ __forceinline__ void warp_stream(const __half* Kb, const __half* Vb, const float* q_heads /* [GQ][128] */,
                                             float scale, int p0, int p1, int warp, int nwarps, unsigned char* wsmem,
-                                            float& m_run, float& l_run, float (&o)[32]) {
+                                            float& m_run, float& l_run, float (&o)[32], bool first_issued = false,
+                                            int fresh_end = 0) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     // Q fragments for the 8 k-steps: a0 = Q[g][16 ks + 2t, +1], a2 = Q[g][16 ks + 8 + 2t, +1]
     uint32_t qh0[8], qh2[8], ql0[8], ql2[8];
@@ -84,20 +101,17 @@ __device__ __forceinline__ void warp_stream(const __half* Kb, const __half* Vb, 
     const uint32_t sbase = smem_u32(wsmem);
     const int ntile = (p1 - p0 + kTile - 1) / kTile;
     // tiles of this warp: warp, warp + nwarps, ...
-    auto issue = [&](int tile_idx, int buf) {
-        const int tpos = p0 + tile_idx * kTile;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int idx = i * 32 + lane;          // 256 chunks per tile
-            const int r = idx >> 4, c = idx & 15;
-            const int pos = min(tpos + r, p1 - 1);  // rows past the end are masked later
-            cp_async16(sbase + buf * 2 * kTileBytes + tile_off(r, c), Kb + (size_t)pos * 128 + c * 8);
-            cp_async16(sbase + buf * 2 * kTileBytes + kTileBytes + tile_off(r, c), Vb + (size_t)pos * 128 + c * 8);
-        }
-        cp_async_commit();
-    };
+    auto issue = [&](int tile_idx, int buf) { issue_tile(Kb, Vb, sbase, buf, p0 + tile_idx * kTile, p1 - 1); };
     int it = 0;
-    if (warp < ntile) issue(warp, 0);
+    // `first_issued`: the caller requested this warp's first tile (rows p0 + 16 warp ...) before it knew the sequence's
+    // position.  The copy is good if all its rows lie below `fresh_end` (the end of the rows that were final then);
+    // otherwise it is requested again (after the first has landed: both write the same buffer).
+    if (first_issued && p0 + (warp + 1) * kTile > fresh_end) {
+        cp_async_wait<0>();
+        __syncwarp();
+        first_issued = false;
+    }
+    if (warp < ntile && !first_issued) issue(warp, 0);
     for (int ti = warp; ti < ntile; ti += nwarps, ++it) {
         const int buf = it & 1;
         if (ti + nwarps < ntile) {
@@ -162,6 +176,7 @@ __device__ __forceinline__ void warp_stream(const __half* Kb, const __half* Vb, 
         }
         __syncwarp();  // the buffer is refilled two iterations later by this same warp
     }
+    cp_async_wait<0>();   // an early first tile this warp turned out not to need
     // the four threads of a head each hold a quarter of the sum
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
