@@ -52,6 +52,9 @@ struct bw_decode {
     float *x = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *gu = nullptr, *logits = nullptr;
     int8_t* attn_q = nullptr;   // attention result block-16 quantized by the attention kernel (int8 mode, fused form)
     float* attn_qs = nullptr;
+    // norm-pending hand-over (one sequence, int8 mode): the hidden state after O (a) and after down (b), quantized
+    int8_t *pa_q = nullptr, *pb_q = nullptr;
+    float *pa_s = nullptr, *pa_ss = nullptr, *pb_s = nullptr, *pb_ss = nullptr;
     int *tokens_in = nullptr, *sampled = nullptr, *pos = nullptr;
     int *prompt = nullptr, *prompt_len = nullptr, *gen = nullptr;
     int max_prompt = 0, max_new = 0;
@@ -197,10 +200,24 @@ int enqueue_step(bw_decode* d, cudaStream_t st) {
     const int M = c.batch, H = c.hidden, nq = c.n_q_heads, nkv = c.n_kv_heads, I = c.inter;
     BW_TRY(bw_select_input_tokens(d->tokens_in, d->sampled, d->prompt, d->prompt_len, d->pos, M, d->max_prompt, st));
     BW_TRY(bw_embed_gather_f32(d->x, d->embed, d->tokens_in, H, c.vocab, M, st));
+    // One sequence in int8 mode: the O and down projections hand their result to the next GEMV already quantized, so
+    // that no CTA of the QKV / gate+up / LM-head GEMVs has to quantize the hidden state (bw_gemv_w4a8_pending).
+    const bool pending = M == 1 && c.act_bits == 8 && (nq / nkv == 4 || nq / nkv == 8) && H % 16 == 0;
+    auto pend = [&](float* y, const float* res, const Mat& W, int N, const int8_t* xq, const float* xs, const float* xss,
+                    const float* gate, const float* up, const float* next_w, int8_t* nq_, float* ns, float* nss) {
+        bw_gemv_pending_args g{};
+        g.y = y; g.residual = res; g.x_q = xq; g.x_scale = xs; g.x_block_sumsq = xss; g.eps = c.eps;
+        g.gate = gate; g.up = up; g.W_packed = W.packed; g.W_scale_f16 = W.sc16; g.K = W.K; g.N = N;
+        g.next_norm_w = next_w; g.next_q = nq_; g.next_scale = ns; g.next_block_sumsq = nss;
+        return bw_gemv_w4a8_pending(&g, st);
+    };
     for (int l = 0; l < c.layers; ++l) {
         const Layer& L = d->layers[l];
         const size_t off = (size_t)l * d->kv_layer;
-        BW_TRY(gemv(d, L.qkv, d->qkv, nullptr, d->x, nullptr, 0, L.rn_in, L.qkv.N, st));
+        if (pending && l > 0)
+            BW_TRY(pend(d->qkv, nullptr, L.qkv, L.qkv.N, d->pb_q, d->pb_s, d->pb_ss, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr));
+        else
+            BW_TRY(gemv(d, L.qkv, d->qkv, nullptr, d->x, nullptr, 0, L.rn_in, L.qkv.N, st));
         const bool fused = nq / nkv == 4 || nq / nkv == 8;
         const bool q8 = fused && c.act_bits == 8;   // the attention kernel quantizes its result for the O projection
         if (q8) {
@@ -216,6 +233,13 @@ int enqueue_step(bw_decode* d, cudaStream_t st) {
             BW_TRY(bw_attention_decode_f16kv(d->attn, d->q, d->kc, d->vc, d->pos, c.max_seq, nq, nkv, 128, c.max_seq, M,
                                              d->kv_batch, off, st));
         }
+        if (pending) {
+            const float* next_w = l + 1 < c.layers ? d->layers[l + 1].rn_in : d->rn_final;
+            BW_TRY(pend(d->x, d->x, L.o, H, d->attn_q, d->attn_qs, nullptr, nullptr, nullptr, L.rn_post, d->pa_q, d->pa_s, d->pa_ss));
+            BW_TRY(pend(d->gu, nullptr, L.gu, 2 * I, d->pa_q, d->pa_s, d->pa_ss, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr));
+            BW_TRY(pend(d->x, d->x, L.down, H, nullptr, nullptr, nullptr, d->gu, d->gu + I, next_w, d->pb_q, d->pb_s, d->pb_ss));
+            continue;
+        }
         if (q8)
             BW_TRY(bw_gemv_w4a8_q8_decode(d->x, 0, d->x, d->attn_q, d->attn_qs, L.o.packed, L.o.sc16, L.o.K, H, M, st));
         else
@@ -223,7 +247,10 @@ int enqueue_step(bw_decode* d, cudaStream_t st) {
         BW_TRY(gemv(d, L.gu, d->gu, nullptr, d->x, nullptr, 0, L.rn_post, 2 * I, st));
         BW_TRY(gemv(d, L.down, d->x, d->x, d->gu, d->gu + I, 2 * (long)I, nullptr, H, st));
     }
-    BW_TRY(gemv(d, d->lm, d->logits, nullptr, d->x, nullptr, 0, d->rn_final, c.vocab, st));
+    if (pending)
+        BW_TRY(pend(d->logits, nullptr, d->lm, c.vocab, d->pb_q, d->pb_s, d->pb_ss, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr));
+    else
+        BW_TRY(gemv(d, d->lm, d->logits, nullptr, d->x, nullptr, 0, d->rn_final, c.vocab, st));
     BW_TRY(bw_sample_argmax_batched(d->logits, c.vocab, c.vocab, M, d->sampled, d->pos, c.max_seq - 1, st));
     BW_TRY(bw_record_generated(d->gen, d->sampled, d->prompt_len, d->pos, M, d->max_new, st));
     return 0;
@@ -242,6 +269,9 @@ int alloc_state(bw_decode* d) {
     BW_TRY(dev_alloc(d, &d->attn, M * (size_t)c.n_q_heads * 128));
     BW_TRY(dev_alloc(d, &d->attn_q, M * (size_t)c.n_q_heads * 128));
     BW_TRY(dev_alloc(d, &d->attn_qs, M * (size_t)c.n_q_heads * 8));
+    BW_TRY(dev_alloc(d, &d->pa_q, H));  BW_TRY(dev_alloc(d, &d->pb_q, H));
+    BW_TRY(dev_alloc(d, &d->pa_s, H / 16 + 1));  BW_TRY(dev_alloc(d, &d->pa_ss, H / 16 + 1));
+    BW_TRY(dev_alloc(d, &d->pb_s, H / 16 + 1));  BW_TRY(dev_alloc(d, &d->pb_ss, H / 16 + 1));
     BW_TRY(dev_alloc(d, &d->gu, M * 2 * (size_t)c.inter));
     BW_TRY(dev_alloc(d, &d->logits, M * (size_t)c.vocab));
     BW_TRY(dev_alloc(d, &d->tokens_in, M));

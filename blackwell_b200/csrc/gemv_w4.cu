@@ -167,9 +167,9 @@ struct StreamPlan {
     size_t smem = 0;
 };
 
-template <int M, typename WS, bool kMulti>
+template <int M, typename WS, bool kMulti, bool kPending = false>
 static cudaError_t launch_stream_inst(const GemvArgs& a, const StreamPlan& p, cudaStream_t st) {
-    auto kern = gemv_w4_stream_kernel<M, WS, kMulti>;
+    auto kern = gemv_w4_stream_kernel<M, WS, kMulti, kPending>;
     static std::once_flag once[kMaxDevices];
     const int dev = current_device();
     cudaError_t attr_err = cudaSuccess;
@@ -250,7 +250,7 @@ static cudaError_t launch_rows(const GemvArgs& a, int M, int row0, int row_count
 static inline bool aligned(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
 
 // Decides whether the streaming kernel can take the launch and with what shape.
-static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
+static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes, int min_row_unit = 1) {
     StreamPlan p;
     const int K = a.K, N = a.N;
     if (g_tune_force_plain.load() || M < 1 || M > 8 || K % 32 != 0 || N < 1) return p;
@@ -304,11 +304,12 @@ static StreamPlan plan_stream(const GemvArgs& a, int M, int ws_bytes) {
     }
     p.S = S;
     p.smem = fixed + (size_t)S * stage;
-    p.row_unit = 1;
-    while ((p.row_unit * row_sc) % 16 != 0) p.row_unit *= 2;
+    int tile_unit = 1;
+    while ((tile_unit * row_sc) % 16 != 0) tile_unit *= 2;
     // Every tile must start on a row whose scale bytes are 16-byte aligned in global memory (the bulk copy's rule):
     // with one row per tile and a scale row of 8 mod 16 bytes, odd tiles would not.  Such shapes take the plain kernel.
-    if ((rg * p.G) % p.row_unit != 0) return p;
+    if ((rg * p.G) % tile_unit != 0) return p;
+    p.row_unit = tile_unit > min_row_unit ? tile_unit : min_row_unit;   // powers of two: the larger is the common multiple
     p.n_rows = N - N % p.row_unit;
     p.ok = p.n_rows > 0;
     return p;
@@ -460,6 +461,19 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
         a.x = xq; a.xsc = xs; a.x2 = nullptr; a.norm_w = nullptr; a.xkind = kXInt8; a.x_stride = a.K;
         if (use_mma && !plan_mma(a, M, (int)sizeof(WS), mp)) use_mma = false;   // the plan depends on the operand kind
     }
+    // Norm-pending hand-over (see GemvArgs): one sequence, dp4a streaming kernel, every row streamed, tiles that are
+    // whole k-blocks of the consumer.  Anything else is refused: the caller chose this form for a shape it knows.
+    if (a.next_q || a.x_sumsq) {
+        if (M != 1 || sizeof(WS) != 2 || a.xkind != kXInt8 || a.K % 32 != 0) return cudaErrorInvalidValue;   // (a SwiGLU
+        // input has been quantized by the prep kernel above)
+        if (a.next_q && (!a.next_sc || !a.next_sumsq || !a.next_norm_w || a.N % 16 != 0)) return cudaErrorInvalidValue;
+        const StreamPlan p = plan_stream(a, 1, (int)sizeof(WS), a.next_q ? 16 : 1);
+        const int R = p.rg * p.G;
+        if (!p.ok || p.n_rows != a.N || (a.next_q && !(R == 8 || R == 16 || R % 32 == 0))) return cudaErrorInvalidValue;
+        a.Tg = p.Tg; a.G = p.G; a.J = p.J; a.S = p.S; a.rg = p.rg;
+        a.row_unit = p.row_unit; a.n_rows = p.n_rows;
+        return p.J > 1 ? launch_stream_inst<1, WS, true, true>(a, p, st) : launch_stream_inst<1, WS, false, true>(a, p, st);
+    }
     if (use_mma) return launch_mma<WS>(a, mp, M, st);
     // Larger batches go to the tcgen05 kernel, up to 64 sequences per launch.
     if (use_tc) {
@@ -605,6 +619,26 @@ extern "C" int bw_gemv_w4a8_q8_decode(float* y_out, long y_stride, const float* 
     a.W = W_packed; a.Wsc = W_scale_f16; a.x = x_q; a.xsc = x_scale;
     a.xkind = kXInt8; a.K = K; a.N = N;
     return gemv_dispatch<__half>(a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bw_gemv_w4a8_pending(const bw_gemv_pending_args* g, void* stream) {
+    if (!g || (!g->x_q && !g->gate)) return cudaErrorInvalidValue;
+    if (g->x_q && (!g->x_scale || g->gate || g->up)) return cudaErrorInvalidValue;
+    if (g->gate && (!g->up || g->x_block_sumsq)) return cudaErrorInvalidValue;
+    if (!g->next_norm_w && !g->x_block_sumsq) return cudaErrorInvalidValue;   // nothing pending: use the plain entries
+    GemvArgs a{};
+    a.y = g->y; a.residual = g->residual;
+    a.W = g->W_packed; a.Wsc = g->W_scale_f16; a.K = g->K; a.N = g->N; a.eps = g->eps;
+    if (g->x_q) {
+        a.x = g->x_q; a.xsc = g->x_scale; a.x_sumsq = g->x_block_sumsq; a.xkind = kXInt8;
+    } else {
+        a.x = g->gate; a.x2 = g->up; a.x_stride = g->K; a.xkind = kXSwiglu;
+    }
+    if (g->next_norm_w) {
+        a.next_norm_w = g->next_norm_w; a.next_q = g->next_q; a.next_sc = g->next_scale; a.next_sumsq = g->next_block_sumsq;
+        if (!a.next_q || !a.next_sc || !a.next_sumsq) return cudaErrorInvalidValue;
+    }
+    return gemv_dispatch<__half>(a, 1, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int bw_gemv_int4_fused(float* y_out, const float* x_f32, const float* up_or_null,

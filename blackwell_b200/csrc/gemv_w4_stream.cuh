@@ -53,6 +53,17 @@ struct GemvArgs {
     const float* norm_w;    // [K] for kXFloatNorm
     const float* residual;  // optional [M][y_stride]: added to the result (may alias y)
     int* status;            // device status word (bw_device_status)
+    // "Norm-pending" hand-over between two GEMVs of a decode step at one sequence (dp4a streaming kernel only).  The
+    // producer's epilogue, which holds 16 consecutive outputs in 16 lanes, also writes what the consumer's fused
+    // RMSNorm + quantize prologue would compute from them, except the norm's scalar: q = q8(y * next_norm_w) with the
+    // block's own scale, and the block's sum of y^2.  The consumer (xkind kXInt8 with x_sumsq set) sums the per-block
+    // sums in fixed order, forms rstd and multiplies it into the block scales: the integers of q8(y * w * rstd) do
+    // not depend on rstd.  Saves every consumer CTA the quantization of all K activations.
+    const float* x_sumsq;       // consumer: [K/16] per-block sums of squares of the un-normed activations, or nullptr
+    const float* next_norm_w;   // producer: [N] norm weights of the consumer, or nullptr
+    int8_t* next_q;             // producer: [N]
+    float* next_sc;             // producer: [N/16] block scales without rstd
+    float* next_sumsq;          // producer: [N/16]
 #ifdef BW_GEMV_TIMELINE
     unsigned long long* timeline;  // experiment builds only: per-phase %globaltimer stamps of a few CTAs
 #endif
@@ -120,7 +131,7 @@ __device__ __forceinline__ void make_xblock(const GemvArgs& a, int m, int kb, fl
         const uint2 q0 = __ldg(p), q1 = __ldg(p + 1);
         e[0] = prmt(q0.x, q0.y, 0x6420); o[0] = prmt(q0.x, q0.y, 0x7531);
         e[1] = prmt(q1.x, q1.y, 0x6420); o[1] = prmt(q1.x, q1.y, 0x7531);
-        s = __ldg(a.xsc + (size_t)m * nkb + kb) * 0.0625f;
+        s = __ldg(a.xsc + (size_t)m * nkb + kb) * 0.0625f * rstd;   // rstd is 1 unless the norm is pending
     } else if (a.xkind == kXInt4) {
         const uint2 q = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(a.x) + (size_t)m * (K / 2) + 8 * (size_t)kb));
         e[0] = bytes_minus8(q.x & 0x0F0F0F0Fu); o[0] = bytes_minus8((q.x >> 4) & 0x0F0F0F0Fu);
@@ -288,7 +299,9 @@ __host__ __device__ inline size_t gemv_x_smem_bytes(int M, int nch, int J) {
 }
 __host__ __device__ inline size_t align128(size_t v) { return (v + 127) & ~(size_t)127; }
 
-template <int M, typename WS, bool kMultiPass>
+// kPending: the instantiation that serves the norm-pending hand-over (one sequence); the ordinary one carries none of
+// its code (the hand-over's extra registers cost the M = 1 kernel 3 % on the small matrices).
+template <int M, typename WS, bool kMultiPass, bool kPending = false>
 __global__ void __launch_bounds__(M <= 2 ? 512 : 256, 1)
 gemv_w4_stream_kernel(const GemvArgs a) {
     constexpr int RG = RowsPerGroup<M>::value;
@@ -368,15 +381,20 @@ gemv_w4_stream_kernel(const GemvArgs a) {
     BW_TL(2);
 
     // ---- activation prologue (overlaps the first weight tiles in flight) ----
-    const bool needs_norm = (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4);
+    const bool pending_norm = kPending && a.x_sumsq != nullptr;   // one sequence: per-block sums of squares from the producer
+    const bool needs_norm = (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4) || pending_norm;
     if (needs_norm) {
         // sum of squares of every sequence, all threads cooperating
         for (int m = 0; m < M; ++m) {
             float ss = 0.f;
-            const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * a.x_stride);
-            for (int i = t; i < K / 4; i += T) {
-                const float4 f = __ldg(p + i);
-                ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); ss = fmaf(f.z, f.z, ss); ss = fmaf(f.w, f.w, ss);
+            if (pending_norm) {
+                for (int i = t; i < K / 16; i += T) ss += __ldcg(a.x_sumsq + i);
+            } else {
+                const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * a.x_stride);
+                for (int i = t; i < K / 4; i += T) {
+                    const float4 f = __ldg(p + i);
+                    ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); ss = fmaf(f.z, f.z, ss); ss = fmaf(f.w, f.w, ss);
+                }
             }
             ss = warp_sum(ss);
             if (lane == 0) wscratch[m * 16 + warp] = ss;
@@ -427,6 +445,7 @@ gemv_w4_stream_kernel(const GemvArgs a) {
 
     // ------------------------------------------------------------- main loop
     bool aborted = false;
+    float held = 0.f;   // norm-pending hand-over with tiles of 8 rows: the even tile's value of this lane
     for (int tile = 0; tile < ntiles; ++tile) {
         const int s = tile % S;
         const uint32_t parity = (uint32_t)(tile / S) & 1u;
@@ -469,12 +488,53 @@ gemv_w4_stream_kernel(const GemvArgs a) {
 
         if (t < R * M) {
             const int r = t / M, m = t - r * M;
+            float val = 0.f;
             if (r < rows) {
                 const int gg = r % G, rr = r / G;
                 float sum = 0.f;
                 for (int w = 0; w < warps_per_group; ++w) sum += redb[(gg * warps_per_group + w) * 32 + rr * M + m];
                 const size_t yi = (size_t)m * a.y_stride + r0 + r;
-                a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
+                val = a.residual ? sum + a.residual[yi] : sum;
+                a.y[yi] = val;
+            }
+            if (kPending && M == 1 && a.next_q) {
+                // Norm-pending hand-over.  The host guarantees row ranges that start at multiples of 16 and hold a
+                // multiple of 16 rows, and tiles of 8, 16 or a multiple of 32 rows: lanes 16 j .. 16 j + 15 hold one
+                // k-block of the consumer, or (tiles of 8, long K) lanes 0..7 hold half of one and keep the even tile's
+                // half until the odd tile arrives.
+                if (R == 8) {
+                    if ((tile & 1) == 0) {
+                        held = val;
+                    } else {
+                        const int col = r0 - 8 + r;          // the first half's row; the second is col + 8
+                        const float v0 = held * __ldg(a.next_norm_w + col), v1 = val * __ldg(a.next_norm_w + col + 8);
+                        float am = fmaxf(fabsf(v0), fabsf(v1)), ss = fmaf(held, held, val * val);
+#pragma unroll
+                        for (int o = 1; o < 8; o <<= 1) {
+                            am = fmaxf(am, __shfl_xor_sync(0xFFu, am, o));
+                            ss += __shfl_xor_sync(0xFFu, ss, o);
+                        }
+                        const float sc = quant_scale_i8(am);
+                        a.next_q[col] = (int8_t)quant_i8(v0, sc);
+                        a.next_q[col + 8] = (int8_t)quant_i8(v1, sc);
+                        if (r == 0) { a.next_sc[col >> 4] = sc; a.next_sumsq[col >> 4] = ss; }
+                    }
+                } else {
+                    const unsigned mask = R == 16 ? 0xFFFFu : 0xFFFFFFFFu;
+                    const int col = r0 + r;
+                    const float v = r < rows ? val * __ldg(a.next_norm_w + col) : 0.f;
+                    float am = fabsf(v), ss = val * val;
+#pragma unroll
+                    for (int o = 1; o < 16; o <<= 1) {
+                        am = fmaxf(am, __shfl_xor_sync(mask, am, o));
+                        ss += __shfl_xor_sync(mask, ss, o);
+                    }
+                    const float sc = quant_scale_i8(am);
+                    if (r < rows) {
+                        a.next_q[col] = (int8_t)quant_i8(v, sc);
+                        if ((r & 15) == 0) { a.next_sc[col >> 4] = sc; a.next_sumsq[col >> 4] = ss; }
+                    }
+                }
             }
         }
     }

@@ -222,6 +222,29 @@ def gemv_w4a8_decode(y_out, y_stride, residual, x_f32, up, x_stride, norm_weight
         C.c_float(eps), _p(W_packed), _p(W_scale_f16), K, N, M, _s(stream)))
 
 
+class _PendingArgs(C.Structure):
+    _fields_ = [("y", C.c_void_p), ("residual", C.c_void_p), ("x_q", C.c_void_p), ("x_scale", C.c_void_p),
+                ("x_block_sumsq", C.c_void_p), ("eps", C.c_float), ("gate", C.c_void_p), ("up", C.c_void_p),
+                ("W_packed", C.c_void_p), ("W_scale_f16", C.c_void_p), ("K", C.c_int), ("N", C.c_int),
+                ("next_norm_w", C.c_void_p), ("next_q", C.c_void_p), ("next_scale", C.c_void_p),
+                ("next_block_sumsq", C.c_void_p)]
+
+
+def gemv_w4a8_pending(y, residual, W_packed, W_scale_f16, K, N, x_q=None, x_scale=None, x_block_sumsq=None, eps=0.0,
+                      gate=None, up=None, next_norm_w=None, next_q=None, next_scale=None, next_block_sumsq=None,
+                      stream=None):
+    """One-sequence GEMV with the norm-pending hand-over (bw_gemv_w4a8_pending)."""
+    def vp(t):
+        if t is None:
+            return None
+        return t if isinstance(t, int) else t.data_ptr()
+
+    a = _PendingArgs(vp(y), vp(residual), vp(x_q), vp(x_scale), vp(x_block_sumsq), float(eps), vp(gate), vp(up),
+                     vp(W_packed), vp(W_scale_f16), K, N, vp(next_norm_w), vp(next_q), vp(next_scale),
+                     vp(next_block_sumsq))
+    _chk("gemv_w4a8_pending", _L.bw_gemv_w4a8_pending(C.byref(a), _s(stream)))
+
+
 def gemv_w4a8_q8_decode(y_out, y_stride, residual, x_q, x_scale, W_packed, W_scale_f16, K, N, M, stream=None):
     _chk("gemv_w4a8_q8_decode", _L.bw_gemv_w4a8_q8_decode(
         _p(y_out), C.c_long(y_stride), _p(residual), _p(x_q), _p(x_scale), _p(W_packed), _p(W_scale_f16), K, N, M,

@@ -85,6 +85,39 @@ int bw_gemv_w4a8_q8_decode(float* y_out, long y_stride, const float* residual_or
                            const float* x_scale, const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N,
                            int M, void* stream);
 
+/* "Norm-pending" hand-over between two GEMVs of a decode step at ONE sequence (no counterpart in the reference).
+ * At one sequence the fused RMSNorm + quantize prologue makes every CTA of a GEMV quantize all K activations.  Here the
+ * GEMV that PRODUCES those activations (O projection, down projection: y = residual + W x) also writes, from the 16
+ * consecutive outputs a tile's epilogue holds, what the consumer's prologue would compute -- except the norm's scalar:
+ *   next_q     i8  [N]     q8(y * next_norm_w), each 16-block with its own scale,
+ *   next_scale f32 [N/16]  those scales (without the norm's 1/rms),
+ *   next_block_sumsq f32 [N/16]  sum of y^2 per block,
+ * and the CONSUMER (x_q = next_q, x_scale = next_scale, x_block_sumsq = next_block_sumsq, eps) sums the block sums in
+ * fixed order, forms 1/rms and multiplies it into the scales: the integers of q8(y w / rms) do not depend on rms.  The
+ * result differs from the fused prologue's only where a product lands on a rounding tie (one more float rounding).
+ * A call is a producer (next_norm_w != NULL), a consumer (x_block_sumsq != NULL) or both.  Input: pre-quantized int8
+ * (x_q, x_scale) or the SwiGLU pair (gate, up f32 [K], x_q == NULL; quantized once by a small kernel first).
+ * Requirements (else cudaErrorInvalidValue): K % 32 == 0, N % 16 == 0 for a producer, 16-byte aligned operands, a shape
+ * the dp4a streaming kernel takes whole. */
+typedef struct {
+    float* y;                       /* [N] */
+    const float* residual;          /* [N] or NULL; may alias y */
+    const int8_t* x_q;              /* [K] or NULL */
+    const float* x_scale;           /* [K/16] */
+    const float* x_block_sumsq;     /* [K/16] or NULL: norm pending on the input */
+    float eps;
+    const float* gate;              /* [K], with x_q == NULL */
+    const float* up;                /* [K] */
+    const uint8_t* W_packed;
+    const uint16_t* W_scale_f16;
+    int K, N;
+    const float* next_norm_w;       /* [N] or NULL */
+    int8_t* next_q;                 /* [N] */
+    float* next_scale;              /* [N/16] */
+    float* next_block_sumsq;        /* [N/16] */
+} bw_gemv_pending_args;
+int bw_gemv_w4a8_pending(const bw_gemv_pending_args* args, void* stream);
+
 /* Reference-format (W4A4, fp32 scales) GEMV with fused prologues: the int4
  * quantize rule of quantize_int4 (kernels.h:800-816) applied to x, to
  * rmsnorm(x) (norm_weight != NULL) or to silu(gate)*up (up != NULL).  M <= 8 (fp32 scales stay on the dp4a
