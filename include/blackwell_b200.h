@@ -382,7 +382,7 @@ int bw_peer_comm_status(void* comm, int* status_out);
 int bw_peer_comm_destroy(void* comm);
 
 /* Library-owned scratch memory.  Two kernel families keep a per-device, grow-only scratch block: the tensor-core
- * GEMV (batches of more than 16 sequences through bw_gemv_w4a8*: prepared activations, K-split partial sums, arrival
+ * GEMV (float-input calls from 2 sequences on: activations quantized once; more than 16 sequences: prepared activations, K-split partial sums, arrival
  * counters) and the allocating attention entry points (split partials, arrival counters).  A block is shared by all
  * streams of the device -- two calls of the same family must not overlap on one GPU -- and grows (cudaMalloc +
  * cudaMemset, synchronising) when a larger problem arrives; an outgrown block stays allocated until the library is
