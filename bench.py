@@ -403,6 +403,44 @@ def run_ours(args, rank, world, local_rank):
             sweep = batch_sweep(dev, state, mats)
         except Exception as exc:
             sweep = [{"error": repr(exc)[:200]}]
+    # ---- N > 1: where the step's time goes -- the five sharded GEMVs without their exchanges, and the two exchanges alone
+    # (each a CUDA graph replayed 200 times between events, max over ranks), beside the whole step
+    tp_break = None
+    if world > 1 and coll is not None and use_graph:
+        def timed_us(fn):
+            fn()
+            barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            for _ in range(3):
+                g.replay()
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(200):
+                g.replay()
+            a1.record()
+            barrier()
+            t = torch.tensor([a0.elapsed_time(a1) / 200 * 1e3], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return round(float(t.item()), 2)
+
+        def gemvs_only():
+            for sh, W, sc, x, y in state:
+                k.gemv_w4a8_f16in(y, x, W, sc, sh.k_local, sh.n_local, M)
+
+        def exchanges_only():
+            for sh, W, sc, x, y in state:
+                if sh.kind == "k":
+                    coll.finish(sh, y)
+
+        try:
+            tp_break = {"step_us": round(sec_per_step * 1e6, 2), "gemvs_without_exchange_us": timed_us(gemvs_only),
+                        "exchanges_alone_us": timed_us(exchanges_only), "exchanges_per_step": sum(1 for st in state if st[0].kind == "k"),
+                        "exchange": args.exchange}
+        except Exception as exc:
+            tp_break = {"error": repr(exc)[:300]}
     # ---- N > 1: the values behind the scaling curve -- a small tensor-parallel decode step against the single-GPU one
     tp_par = None
     if world > 1 and not args.only:
@@ -461,6 +499,7 @@ def run_ours(args, rank, world, local_rank):
         "per_matrix_batched": per_batched,
         "batch_sweep": sweep,
         "tp_parity": tp_par,
+        "tp_breakdown": tp_break,
         "decode": decode,
     }
     print(json.dumps(line), flush=True)
