@@ -411,7 +411,8 @@ int bw_reserve_scratch(size_t gemv_bytes, size_t attention_bytes);
  * kernel (0 = off; bits: 1 no epilogue arithmetic, 2 no unpack, 4 no weight loads, 8 no MMAs, 16 / 32 no activation /
  * activation-scale copies, 64 no weight-scale loads: results are then meaningless), key 20 = smallest batch whose
  * float activations are quantized once by a separate kernel before a streaming GEMV (0 = default 2), key 21 = the
- * same for the SwiGLU prologue (0 = default 1). */
+ * same for the SwiGLU prologue (0 = default 1), key 22 = decode attention: the earlier split rule with pct % of the SMs
+ * as CTA slots (0 = default rule: one wave of two CTAs per SM, at least 224 positions per split). */
 int bw_set_tuning(int key, int value);
 /* Number of kernels launched by this library since the last call with reset != 0. */
 long long bw_launch_count(int reset);
