@@ -466,6 +466,14 @@ def run_ours(args, rank, world, local_rank):
                 decode.append(run_decode(shapes.QWEN3_32B, 64, 4096, 5, dev, world, rank, exchange=args.exchange))
             except Exception as exc:
                 decode.append({"model": shapes.QWEN3_32B.name, "batch": 64, "error": repr(exc)[:200]})
+    # ---- decode attention on its own (1 GPU): the binary16-cache kernel of the decode step and the reference-format
+    # fp32-cache entry point, each launch over another layer of a cache larger than L2
+    attention = []
+    if rank == 0 and world == 1 and not args.only and not args.no_decode:
+        try:
+            attention = attention_records(dev)
+        except Exception as exc:
+            attention = [{"error": repr(exc)[:200]}]
     if rank != 0:
         return
     peak, peak_kind = measured_peak()
@@ -500,6 +508,7 @@ def run_ours(args, rank, world, local_rank):
         "batch_sweep": sweep,
         "tp_parity": tp_par,
         "tp_breakdown": tp_break,
+        "attention": attention,
         "decode": decode,
     }
     print(json.dumps(line), flush=True)
@@ -669,6 +678,47 @@ def config0_record(dev):
             "parity": {"max_abs_rel_vs_f64_oracle": mar, "block_dots_bit_exact": dots_equal},
             "cpu_port": {"single_thread_us": round((t1 - t0) * 1e6, 1), "all_core_us": round((t3 - t2) * 1e6, 1),
                          "cores": cores}}
+
+
+def attention_records(dev):
+    """Decode attention alone, L2-cold (a CUDA graph of 24 launches rotating over the layers of one cache): time,
+    K/V bytes per second and the fraction of the measured HBM peak.  `f16` is the fused tensor-core form the decode
+    step uses (head norm, RoPE, KV write and int8 output included), `f32` the reference-format entry point
+    (attention_decode_batched_gqa_device: fp32 cache, scalar kernel)."""
+    import torch
+
+    from blackwell_b200 import kernels as k
+
+    peak, _ = measured_peak()
+    out = []
+    for kind, M, nq, nkv, ctx, layers in [("f16", 1, 32, 8, 2048, 24), ("f16", 8, 32, 8, 2048, 12),
+                                          ("f16", 64, 64, 8, 4096, 3), ("f32", 1, 32, 8, 2048, 24),
+                                          ("f32", 8, 32, 8, 2048, 6)]:
+        max_seq = ctx + 16
+        kv_layer = nkv * max_seq * 128
+        dt = torch.float16 if kind == "f16" else torch.float32
+        kc = torch.randn((M, layers * kv_layer), device=dev, dtype=dt) * 0.5
+        vc = torch.randn((M, layers * kv_layer), device=dev, dtype=dt) * 0.5
+        pos = torch.full((M,), ctx - 1, device=dev, dtype=torch.int32)
+        o = torch.empty((M, nq * 128), device=dev, dtype=torch.float32)
+        if kind == "f16":
+            qkv = torch.randn((M, (nq + 2 * nkv) * 128), device=dev, dtype=torch.float32)
+            qn, kn = torch.ones(128, device=dev), torch.ones(128, device=dev)
+            oq = torch.empty((M, nq * 128), device=dev, dtype=torch.int8)
+            os_ = torch.empty((M, nq * 8), device=dev, dtype=torch.float32)
+            us = _graph_us(lambda j: k.attention_decode_f16kv_fused_q8(
+                None, oq, os_, qkv, qn, kn, kc, vc, pos, ctx, nq, nkv, 128, max_seq, M, layers * kv_layer,
+                (j % layers) * kv_layer, 1e-6, 1e6), 24)
+        else:
+            q = torch.randn((M, nq * 128), device=dev, dtype=torch.float32)
+            us = _graph_us(lambda j: k.attention_decode_batched_gqa_device(
+                o, q, kc, vc, pos, nq, nkv, 128, max_seq, M, layers * kv_layer, (j % layers) * kv_layer), 24)
+        nbytes = M * nkv * ctx * 128 * 2 * kc.element_size()
+        out.append({"cache": kind, "batch": M, "heads": "%d/%d" % (nq, nkv), "ctx": ctx, "us": round(us, 2),
+                    "kv_gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / peak, 3)})
+        del kc, vc
+        torch.cuda.empty_cache()
+    return out
 
 
 def tp_parity(dev, world, rank):
