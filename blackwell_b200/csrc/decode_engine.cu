@@ -200,7 +200,7 @@ int enqueue_step(bw_decode* d, cudaStream_t st) {
     const int M = c.batch, H = c.hidden, nq = c.n_q_heads, nkv = c.n_kv_heads, I = c.inter;
     BW_TRY(bw_select_input_tokens(d->tokens_in, d->sampled, d->prompt, d->prompt_len, d->pos, M, d->max_prompt, st));
     BW_TRY(bw_embed_gather_f32(d->x, d->embed, d->tokens_in, H, c.vocab, M, st));
-    // One sequence in int8 mode: the O and down projections hand their result to the next GEMV already quantized, so
+    // One sequence in int8 mode (at 5..16 the same hand-over measured no faster than the prep launches): the O and down projections hand their result to the next GEMV already quantized, so
     // that no CTA of the QKV / gate+up / LM-head GEMVs has to quantize the hidden state (bw_gemv_w4a8_pending).
     const bool pending = M == 1 && c.act_bits == 8 && (nq / nkv == 4 || nq / nkv == 8) && H % 16 == 0;
     auto pend = [&](float* y, const float* res, const Mat& W, int N, const int8_t* xq, const float* xs, const float* xss,
@@ -209,6 +209,7 @@ int enqueue_step(bw_decode* d, cudaStream_t st) {
         g.y = y; g.residual = res; g.x_q = xq; g.x_scale = xs; g.x_block_sumsq = xss; g.eps = c.eps;
         g.gate = gate; g.up = up; g.W_packed = W.packed; g.W_scale_f16 = W.sc16; g.K = W.K; g.N = N;
         g.next_norm_w = next_w; g.next_q = nq_; g.next_scale = ns; g.next_block_sumsq = nss;
+        g.M = M; g.x_stride = gate ? 2 * (long)I : 0;
         return bw_gemv_w4a8_pending(&g, st);
     };
     for (int l = 0; l < c.layers; ++l) {
@@ -269,9 +270,9 @@ int alloc_state(bw_decode* d) {
     BW_TRY(dev_alloc(d, &d->attn, M * (size_t)c.n_q_heads * 128));
     BW_TRY(dev_alloc(d, &d->attn_q, M * (size_t)c.n_q_heads * 128));
     BW_TRY(dev_alloc(d, &d->attn_qs, M * (size_t)c.n_q_heads * 8));
-    BW_TRY(dev_alloc(d, &d->pa_q, H));  BW_TRY(dev_alloc(d, &d->pb_q, H));
-    BW_TRY(dev_alloc(d, &d->pa_s, H / 16 + 1));  BW_TRY(dev_alloc(d, &d->pa_ss, H / 16 + 1));
-    BW_TRY(dev_alloc(d, &d->pb_s, H / 16 + 1));  BW_TRY(dev_alloc(d, &d->pb_ss, H / 16 + 1));
+    BW_TRY(dev_alloc(d, &d->pa_q, M * H));  BW_TRY(dev_alloc(d, &d->pb_q, M * H));
+    BW_TRY(dev_alloc(d, &d->pa_s, M * (H / 16 + 1)));  BW_TRY(dev_alloc(d, &d->pa_ss, M * (H / 16 + 1)));
+    BW_TRY(dev_alloc(d, &d->pb_s, M * (H / 16 + 1)));  BW_TRY(dev_alloc(d, &d->pb_ss, M * (H / 16 + 1)));
     BW_TRY(dev_alloc(d, &d->gu, M * 2 * (size_t)c.inter));
     BW_TRY(dev_alloc(d, &d->logits, M * (size_t)c.vocab));
     BW_TRY(dev_alloc(d, &d->tokens_in, M));

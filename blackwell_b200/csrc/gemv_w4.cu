@@ -392,9 +392,9 @@ static bool plan_mma(const GemvArgs& a, int M, int ws_bytes, mma::MmaPlan& p) {
     return plan_mma_slab(a, M, ws_bytes, 64, p, &whole);
 }
 
-template <int MG, typename WS, bool kPack>
+template <int MG, typename WS, bool kPack, bool kPending = false>
 static cudaError_t launch_mma_inst(const GemvArgs& a, const mma::MmaPlan& p, int M, cudaStream_t st) {
-    auto kern = mma::gemv_w4_mma_kernel<MG, WS, kPack>;
+    auto kern = mma::gemv_w4_mma_kernel<MG, WS, kPack, kPending>;
     static std::once_flag once[kMaxDevices];
     const int dev = current_device();
     cudaError_t attr_err = cudaSuccess;
@@ -461,18 +461,26 @@ static cudaError_t gemv_dispatch(GemvArgs a, int M, cudaStream_t st) {
         a.x = xq; a.xsc = xs; a.x2 = nullptr; a.norm_w = nullptr; a.xkind = kXInt8; a.x_stride = a.K;
         if (use_mma && !plan_mma(a, M, (int)sizeof(WS), mp)) use_mma = false;   // the plan depends on the operand kind
     }
-    // Norm-pending hand-over (see GemvArgs): one sequence, dp4a streaming kernel, every row streamed, tiles that are
-    // whole k-blocks of the consumer.  Anything else is refused: the caller chose this form for a shape it knows.
+    // Norm-pending hand-over (see GemvArgs): one sequence on the dp4a streaming kernel (every row streamed, tiles that
+    // are whole or half k-blocks of the consumer), 5..16 sequences on the mma.sync kernel (a producer needs all of K in
+    // one window).  Anything else is refused: the caller chose this form for a shape it knows.
     if (a.next_q || a.x_sumsq) {
-        if (M != 1 || sizeof(WS) != 2 || a.xkind != kXInt8 || a.K % 32 != 0) return cudaErrorInvalidValue;   // (a SwiGLU
-        // input has been quantized by the prep kernel above)
+        if (sizeof(WS) != 2 || a.xkind != kXInt8 || a.K % 32 != 0) return cudaErrorInvalidValue;   // (a SwiGLU input
+        // has been quantized by the prep kernel above)
         if (a.next_q && (!a.next_sc || !a.next_sumsq || !a.next_norm_w || a.N % 16 != 0)) return cudaErrorInvalidValue;
-        const StreamPlan p = plan_stream(a, 1, (int)sizeof(WS), a.next_q ? 16 : 1);
-        const int R = p.rg * p.G;
-        if (!p.ok || p.n_rows != a.N || (a.next_q && !(R == 8 || R == 16 || R % 32 == 0))) return cudaErrorInvalidValue;
-        a.Tg = p.Tg; a.G = p.G; a.J = p.J; a.S = p.S; a.rg = p.rg;
-        a.row_unit = p.row_unit; a.n_rows = p.n_rows;
-        return p.J > 1 ? launch_stream_inst<1, WS, true, true>(a, p, st) : launch_stream_inst<1, WS, false, true>(a, p, st);
+        if (M == 1) {
+            const StreamPlan p = plan_stream(a, 1, (int)sizeof(WS), a.next_q ? 16 : 1);
+            const int R = p.rg * p.G;
+            if (!p.ok || p.n_rows != a.N || (a.next_q && !(R == 8 || R == 16 || R % 32 == 0))) return cudaErrorInvalidValue;
+            a.Tg = p.Tg; a.G = p.G; a.J = p.J; a.S = p.S; a.rg = p.rg;
+            a.row_unit = p.row_unit; a.n_rows = p.n_rows;
+            return p.J > 1 ? launch_stream_inst<1, WS, true, true>(a, p, st) : launch_stream_inst<1, WS, false, true>(a, p, st);
+        }
+        if (M < 5 || M > 16) return cudaErrorInvalidValue;
+        mma::MmaPlan pp;
+        if (!plan_mma(a, M, (int)sizeof(WS), pp)) return cudaErrorInvalidValue;
+        if (a.next_q && pp.win_cols < a.K / 32) return cudaErrorInvalidValue;
+        return M <= 8 ? launch_mma_inst<1, WS, false, true>(a, pp, M, st) : launch_mma_inst<2, WS, false, true>(a, pp, M, st);
     }
     if (use_mma) return launch_mma<WS>(a, mp, M, st);
     // Larger batches go to the tcgen05 kernel, up to 64 sequences per launch.
@@ -626,19 +634,20 @@ extern "C" int bw_gemv_w4a8_pending(const bw_gemv_pending_args* g, void* stream)
     if (g->x_q && (!g->x_scale || g->gate || g->up)) return cudaErrorInvalidValue;
     if (g->gate && (!g->up || g->x_block_sumsq)) return cudaErrorInvalidValue;
     if (!g->next_norm_w && !g->x_block_sumsq) return cudaErrorInvalidValue;   // nothing pending: use the plain entries
+    const int M = g->M > 0 ? g->M : 1;
     GemvArgs a{};
     a.y = g->y; a.residual = g->residual;
     a.W = g->W_packed; a.Wsc = g->W_scale_f16; a.K = g->K; a.N = g->N; a.eps = g->eps;
     if (g->x_q) {
         a.x = g->x_q; a.xsc = g->x_scale; a.x_sumsq = g->x_block_sumsq; a.xkind = kXInt8;
     } else {
-        a.x = g->gate; a.x2 = g->up; a.x_stride = g->K; a.xkind = kXSwiglu;
+        a.x = g->gate; a.x2 = g->up; a.x_stride = g->x_stride > 0 ? g->x_stride : g->K; a.xkind = kXSwiglu;
     }
     if (g->next_norm_w) {
         a.next_norm_w = g->next_norm_w; a.next_q = g->next_q; a.next_sc = g->next_scale; a.next_sumsq = g->next_block_sumsq;
         if (!a.next_q || !a.next_sc || !a.next_sumsq) return cudaErrorInvalidValue;
     }
-    return gemv_dispatch<__half>(a, 1, static_cast<cudaStream_t>(stream));
+    return gemv_dispatch<__half>(a, M, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int bw_gemv_int4_fused(float* y_out, const float* x_f32, const float* up_or_null,

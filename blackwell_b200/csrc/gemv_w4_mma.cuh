@@ -112,7 +112,10 @@ template <> struct ScalePairF<float> {
 // are the four sequences against the first k-block (other half of K zero) and the same four against the second, so
 // ONE instruction per 16 rows yields both blocks' dots; the accumulators of the two blocks of a (row, sequence) then
 // sit in two threads and meet in the cross-warp sum.
-template <int MG, typename WS, bool kPack>
+// kPending: the instantiation that serves the norm-pending hand-over (see GemvArgs), here for 5..16 sequences: the
+// tile's 32 rows of one sequence sit in the 32 lanes of a warp when y is written, so a half warp holds one k-block of the
+// consumer.  Row ranges then start at multiples of 16 and K must fit one window.
+template <int MG, typename WS, bool kPack, bool kPending = false>
 __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs a, const MmaPlan p, int M) {
     static_assert(!kPack || MG == 1, "packing is for one group of sequences");
     extern __shared__ __align__(128) unsigned char smem[];
@@ -130,8 +133,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
     const size_t stage_bytes = stage_sc + (size_t)kRows * p.pitch_s;
 
     // this CTA's rows
-    const int row_begin = (int)(((long long)a.N * blockIdx.x) / gridDim.x);
-    const int row_end = (int)(((long long)a.N * (blockIdx.x + 1)) / gridDim.x);
+    const int row_unit = (kPending && a.next_q) ? 16 : 1;   // a producer's row ranges are whole k-blocks of its consumer
+    const int row_begin = row_unit * (int)(((long long)(a.N / row_unit) * blockIdx.x) / gridDim.x);
+    const int row_end = row_unit * (int)(((long long)(a.N / row_unit) * (blockIdx.x + 1)) / gridDim.x);
     const int ntiles = (row_end - row_begin + kRows - 1) / kRows;
     const int nwin = (nch + p.win_cols - 1) / p.win_cols;
 
@@ -221,8 +225,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
         const int wc0 = w * p.win_cols, wc1 = min(nch, wc0 + p.win_cols);
         // ---- prepare the window's activations: B fragments in k-slot order and block scales / 16
         if (w > 0) consumer_sync();  // every warp is done with the previous window's fragments
-        const bool needs_norm = (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4);
-        if (needs_norm && w == 0) {
+        const bool pending_in = kPending && a.x_sumsq != nullptr;   // per-block sums of squares from the producer
+        const bool needs_norm = (a.xkind == kXFloatNorm || a.xkind == kXFloatNormI4) || pending_in;
+        if (pending_in && w == 0) {
+            // one warp per sequence, all loads of a lane independent: a loop over the sequences would pay an L2 round
+            // trip each (measured: 3 us at 8 sequences)
+            if (warp < M) {
+                float ss = 0.f;
+                for (int i = lane; i < K / 16; i += 32) ss += __ldcg(a.x_sumsq + (size_t)warp * (K / 16) + i);
+                ss = warp_sum(ss);   // fixed order: deterministic
+                if (lane == 0) rstd_s[warp] = rsqrtf(ss / (float)K + a.eps);
+            }
+            consumer_sync();
+        } else if (needs_norm && w == 0) {
             for (int m = 0; m < M; ++m) {
                 float ss = 0.f;
                 const float4* px = reinterpret_cast<const float4*>(static_cast<const float*>(a.x) + (size_t)m * a.x_stride);
@@ -389,8 +404,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
             if (*abort_flag) ok = false;
             if (ok) {
                 for (int o = ct; o < kRows * (kPack ? 4 : 8 * MG); o += kConsumerWarps * 32) {
-                    const int row = o & (kRows - 1), m = o >> 5;
-                    if (row < rows && m < M) {
+                    const int row = o & (kRows - 1), m = o >> 5;   // a warp: the 32 rows of one sequence
+                    const bool valid = row < rows && m < M;
+                    float val = 0.f;
+                    if (valid) {
                         float sum = 0.f;
 #pragma unroll
                         for (int wv = 0; wv < kConsumerWarps; ++wv) {
@@ -398,8 +415,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_w4_mma_kernel(const GemvArgs
                             sum += kPack ? rp[0] + rp[4] : rp[0];  // packed: first block's column + second block's
                         }
                         const size_t yi = (size_t)m * a.y_stride + r0 + row;
-                        if (w == 0) a.y[yi] = a.residual ? sum + a.residual[yi] : sum;
+                        if (w == 0) { val = a.residual ? sum + a.residual[yi] : sum; a.y[yi] = val; }
                         else a.y[yi] += sum;
+                    }
+                    if (kPending && a.next_q && m < M) {   // one window of K (the host's rule): val is final
+                        const int col = r0 + row;
+                        const float v = valid ? val * __ldg(a.next_norm_w + col) : 0.f;
+                        float am = fabsf(v), ss = val * val;
+#pragma unroll
+                        for (int sh = 1; sh < 16; sh <<= 1) {
+                            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, sh));
+                            ss += __shfl_xor_sync(0xffffffffu, ss, sh);
+                        }
+                        const float sc = quant_scale_i8(am);
+                        if (valid) {
+                            a.next_q[(size_t)m * a.N + col] = (int8_t)quant_i8(v, sc);
+                            if ((row & 15) == 0) {
+                                a.next_sc[(size_t)m * (a.N / 16) + (col >> 4)] = sc;
+                                a.next_sumsq[(size_t)m * (a.N / 16) + (col >> 4)] = ss;
+                            }
+                        }
                     }
                 }
             }

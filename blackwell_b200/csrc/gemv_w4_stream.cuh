@@ -53,7 +53,8 @@ struct GemvArgs {
     const float* norm_w;    // [K] for kXFloatNorm
     const float* residual;  // optional [M][y_stride]: added to the result (may alias y)
     int* status;            // device status word (bw_device_status)
-    // "Norm-pending" hand-over between two GEMVs of a decode step at one sequence (dp4a streaming kernel only).  The
+    // "Norm-pending" hand-over between two GEMVs of a decode step (dp4a streaming kernel at one sequence, mma.sync
+    // streaming kernel at 5..16; the arrays below then have a leading dimension of M sequences).  The
     // producer's epilogue, which holds 16 consecutive outputs in 16 lanes, also writes what the consumer's fused
     // RMSNorm + quantize prologue would compute from them, except the norm's scalar: q = q8(y * next_norm_w) with the
     // block's own scale, and the block's sum of y^2.  The consumer (xkind kXInt8 with x_sumsq set) sums the per-block

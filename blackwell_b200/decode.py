@@ -90,9 +90,9 @@ class DecodeEngine:
         self.attn_q = torch.zeros((M, self.nq * 128), dtype=torch.int8, device=dev)      # the same, block-16 int8
         self.attn_qs = torch.zeros((M, self.nq * 8), dtype=f32, device=dev)
         # norm-pending hand-over between the GEMVs of a step (one sequence, one GPU): two sets, x after O and after down
-        self.pend = [(torch.zeros(self.s.hidden, dtype=torch.int8, device=dev),
-                      torch.zeros(self.s.hidden // 16, dtype=f32, device=dev),
-                      torch.zeros(self.s.hidden // 16, dtype=f32, device=dev)) for _ in range(2)]
+        self.pend = [(torch.zeros((M, self.s.hidden), dtype=torch.int8, device=dev),
+                      torch.zeros((M, self.s.hidden // 16), dtype=f32, device=dev),
+                      torch.zeros((M, self.s.hidden // 16), dtype=f32, device=dev)) for _ in range(2)]
         self.gu = torch.zeros((M, 2 * self.i_local), dtype=f32, device=dev)
         self.part = torch.zeros((M, H), dtype=f32, device=dev)
         self.logits = torch.zeros((M, self.v_local), dtype=f32, device=dev)
@@ -202,14 +202,15 @@ class DecodeEngine:
         eps = s.eps
         k.embed_gather_f16(self.x, self.embed, self.tokens, H, s.vocab, M)
         # One sequence on one GPU: the O and down projections hand their result to the next GEMV already quantized
-        # (bw_gemv_w4a8_pending), so that no CTA of the QKV / gate+up / LM-head GEMVs quantizes the hidden state.
+        # (bw_gemv_w4a8_pending), so that no CTA of the QKV / gate+up / LM-head GEMVs quantizes the hidden state.  (The
+        # entry point also serves 5..16 sequences; there the hand-over measured no faster than the prep launches.)
         pending = M == 1 and self.world == 1 and self.nq // self.nkv in (4, 8) and H % 16 == 0
         pa, pb = self.pend
         for l, L in enumerate(self.layers):
             off = l * self.kv_layer
             if pending and l > 0:
                 k.gemv_w4a8_pending(self.qkv, None, L["qkv"][0], L["qkv"][1], H, self.qkv_n, x_q=pb[0], x_scale=pb[1],
-                                    x_block_sumsq=pb[2], eps=eps)
+                                    x_block_sumsq=pb[2], eps=eps, M=M)
             else:
                 k.gemv_w4a8_decode(self.qkv, 0, None, self.x, None, 0, L["rn_in"], eps, L["qkv"][0], L["qkv"][1], H,
                                    self.qkv_n, M)
@@ -234,7 +235,7 @@ class DecodeEngine:
             if pending:
                 k.gemv_w4a8_pending(self.x, self.x, L["o"][0], L["o"][1], self.nq * 128, H, x_q=self.attn_q,
                                     x_scale=self.attn_qs, next_norm_w=L["rn_post"], next_q=pa[0], next_scale=pa[1],
-                                    next_block_sumsq=pa[2])
+                                    next_block_sumsq=pa[2], M=M)
             elif self.world == 1:
                 o_proj(self.x, self.x)
             else:
@@ -243,7 +244,7 @@ class DecodeEngine:
                 self._exchange(part)
             if pending:
                 k.gemv_w4a8_pending(self.gu, None, L["gu"][0], L["gu"][1], H, 2 * self.i_local, x_q=pa[0],
-                                    x_scale=pa[1], x_block_sumsq=pa[2], eps=eps)
+                                    x_scale=pa[1], x_block_sumsq=pa[2], eps=eps, M=M)
             else:
                 k.gemv_w4a8_decode(self.gu, 0, None, self.x, None, 0, L["rn_post"], eps, L["gu"][0], L["gu"][1], H,
                                    2 * self.i_local, M)
@@ -252,7 +253,7 @@ class DecodeEngine:
                 nxt = self.layers[l + 1]["rn_in"] if l + 1 < len(self.layers) else self.rn_final
                 k.gemv_w4a8_pending(self.x, self.x, L["down"][0], L["down"][1], self.i_local, H, gate=gate,
                                     up=up.data_ptr(), next_norm_w=nxt, next_q=pb[0], next_scale=pb[1],
-                                    next_block_sumsq=pb[2])
+                                    next_block_sumsq=pb[2], M=M, x_stride=2 * self.i_local)
             elif self.world == 1:
                 k.gemv_w4a8_decode(self.x, 0, self.x, gate, up.data_ptr(), 2 * self.i_local, None, 0.0, L["down"][0],
                                    L["down"][1], self.i_local, H, M)
@@ -264,7 +265,7 @@ class DecodeEngine:
                 self._exchange(part)
         if pending:
             k.gemv_w4a8_pending(self.logits, None, self.lm[0], self.lm[1], H, self.v_local, x_q=pb[0], x_scale=pb[1],
-                                x_block_sumsq=pb[2], eps=eps)
+                                x_block_sumsq=pb[2], eps=eps, M=M)
         else:
             k.gemv_w4a8_decode(self.logits, 0, None, self.x, None, 0, self.rn_final, eps, self.lm[0], self.lm[1], H,
                                self.v_local, M)

@@ -227,13 +227,13 @@ class _PendingArgs(C.Structure):
                 ("x_block_sumsq", C.c_void_p), ("eps", C.c_float), ("gate", C.c_void_p), ("up", C.c_void_p),
                 ("W_packed", C.c_void_p), ("W_scale_f16", C.c_void_p), ("K", C.c_int), ("N", C.c_int),
                 ("next_norm_w", C.c_void_p), ("next_q", C.c_void_p), ("next_scale", C.c_void_p),
-                ("next_block_sumsq", C.c_void_p)]
+                ("next_block_sumsq", C.c_void_p), ("M", C.c_int), ("x_stride", C.c_long)]
 
 
 def gemv_w4a8_pending(y, residual, W_packed, W_scale_f16, K, N, x_q=None, x_scale=None, x_block_sumsq=None, eps=0.0,
                       gate=None, up=None, next_norm_w=None, next_q=None, next_scale=None, next_block_sumsq=None,
-                      stream=None):
-    """One-sequence GEMV with the norm-pending hand-over (bw_gemv_w4a8_pending)."""
+                      M=1, x_stride=0, stream=None):
+    """GEMV with the norm-pending hand-over (bw_gemv_w4a8_pending), 1 or 5..16 sequences."""
     def vp(t):
         if t is None:
             return None
@@ -241,7 +241,7 @@ def gemv_w4a8_pending(y, residual, W_packed, W_scale_f16, K, N, x_q=None, x_scal
 
     a = _PendingArgs(vp(y), vp(residual), vp(x_q), vp(x_scale), vp(x_block_sumsq), float(eps), vp(gate), vp(up),
                      vp(W_packed), vp(W_scale_f16), K, N, vp(next_norm_w), vp(next_q), vp(next_scale),
-                     vp(next_block_sumsq))
+                     vp(next_block_sumsq), int(M), int(x_stride))
     _chk("gemv_w4a8_pending", _L.bw_gemv_w4a8_pending(C.byref(a), _s(stream)))
 
 

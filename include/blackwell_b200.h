@@ -85,8 +85,8 @@ int bw_gemv_w4a8_q8_decode(float* y_out, long y_stride, const float* residual_or
                            const float* x_scale, const uint8_t* W_packed, const uint16_t* W_scale_f16, int K, int N,
                            int M, void* stream);
 
-/* "Norm-pending" hand-over between two GEMVs of a decode step at ONE sequence (no counterpart in the reference).
- * At one sequence the fused RMSNorm + quantize prologue makes every CTA of a GEMV quantize all K activations.  Here the
+/* "Norm-pending" hand-over between two GEMVs of a decode step, at one sequence or 5..16 (no counterpart in the
+ * reference).  The fused RMSNorm + quantize prologue makes every CTA of a GEMV quantize all M x K activations.  Here the
  * GEMV that PRODUCES those activations (O projection, down projection: y = residual + W x) also writes, from the 16
  * consecutive outputs a tile's epilogue holds, what the consumer's prologue would compute -- except the norm's scalar:
  *   next_q     i8  [N]     q8(y * next_norm_w), each 16-block with its own scale,
@@ -115,6 +115,10 @@ typedef struct {
     int8_t* next_q;                 /* [N] */
     float* next_scale;              /* [N/16] */
     float* next_block_sumsq;        /* [N/16] */
+    int M;                          /* sequences: 0 or 1 (dp4a kernel), or 5..16 (mma.sync kernel; every array above then
+                                       has a leading dimension of M, y and residual [M][N], and a producer needs a K that
+                                       the kernel prepares in one window: up to ~12,000 at 8 sequences) */
+    long x_stride;                  /* elements between sequences of gate / up (0 = K) */
 } bw_gemv_pending_args;
 int bw_gemv_w4a8_pending(const bw_gemv_pending_args* args, void* stream);
 

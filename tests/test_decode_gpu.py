@@ -318,52 +318,54 @@ def test_gemv_decode_entry_residual_and_strides(cuda):
     assert np.array_equal(out[:, N:], res[:, N:])  # the padding columns are untouched
 
 
-@pytest.mark.parametrize("from_swiglu,K1", [(False, 1024), (True, 1024), (True, 12288)])
-def test_norm_pending_hand_over_between_two_gemvs(cuda, from_swiglu, K1):
-    """bw_gemv_w4a8_pending at one sequence: the producer (y = residual + W1 x) also emits q8(y * w_norm) block by
-    block and the blocks' sums of y^2; the consumer applies 1/rms to the block scales.  The emitted integers and scales
-    are those of the quantize rule on y * w_norm (bit for bit), and the consumer's output is W2 . q8(rmsnorm(y, w_norm))
-    within the tolerance of the fused-norm prologue (one float rounding more)."""
+@pytest.mark.parametrize("M,from_swiglu,K1", [(1, False, 1024), (1, True, 1024), (1, True, 12288), (8, False, 1024),
+                                              (8, True, 12288), (5, True, 2048)])
+def test_norm_pending_hand_over_between_two_gemvs(cuda, M, from_swiglu, K1):
+    """bw_gemv_w4a8_pending at one sequence (dp4a kernel) and at 5..8 (mma.sync kernel): the producer
+    (y = residual + W1 x) also emits q8(y * w_norm) block by block and the blocks' sums of y^2; the consumer applies
+    1/rms to the block scales.  The emitted integers and scales are those of the quantize rule on y * w_norm (bit for
+    bit), and the consumer's output is W2 . q8(rmsnorm(y, w_norm)) within the tolerance of the fused-norm prologue (one
+    float rounding more).  K1 = 12288 at one sequence: the producer's tiles hold 8 rows, half a block of the consumer."""
     import torch
 
     from blackwell_b200 import kernels as k
 
-    H, N2, eps = 512, 300, 1e-6   # K1 = 12288: the producer's tiles hold 8 rows, half a block of the consumer
+    H, N2, eps = 512, 300, 1e-6
     W1, s1, _ = synth.int4_weights(H, K1, 470)
     W2, s2, _ = synth.int4_weights(N2, H, 471)
-    res = synth.activations_f16(1, H, 472).astype(np.float32)
+    res = synth.activations_f16(M, H, 472).astype(np.float32)
     nw = synth.norm_weight(H, 473)
     W1d, s1d, W2d, s2d = to_dev(W1), to_dev(s1.view(np.uint16)), to_dev(W2), to_dev(s2.view(np.uint16))
     y = to_dev(res.copy())
-    nq = torch.zeros(H, dtype=torch.int8, device="cuda")
-    ns = torch.zeros(H // 16, dtype=torch.float32, device="cuda")
-    nss = torch.zeros(H // 16, dtype=torch.float32, device="cuda")
+    nq = torch.zeros((M, H), dtype=torch.int8, device="cuda")
+    ns = torch.zeros((M, H // 16), dtype=torch.float32, device="cuda")
+    nss = torch.zeros((M, H // 16), dtype=torch.float32, device="cuda")
     if from_swiglu:
-        gu = synth.activations_f16(1, 2 * K1, 474).astype(np.float32)
+        gu = synth.activations_f16(M, 2 * K1, 474).astype(np.float32)
         gud = to_dev(gu)
         k.gemv_w4a8_pending(y, y, W1d, s1d, K1, H, gate=gud, up=gud[:, K1:].data_ptr(), next_norm_w=to_dev(nw), next_q=nq,
-                            next_scale=ns, next_block_sumsq=nss)
+                            next_scale=ns, next_block_sumsq=nss, M=M, x_stride=2 * K1)
         x1 = oracle.swiglu(np.ascontiguousarray(gu[:, :K1]), np.ascontiguousarray(gu[:, K1:]))
     else:
-        x1 = synth.activations_f16(1, K1, 475).astype(np.float32)
+        x1 = synth.activations_f16(M, K1, 475).astype(np.float32)
         xq, xs = oracle.quantize_int8(x1)
         k.gemv_w4a8_pending(y, y, W1d, s1d, K1, H, x_q=to_dev(xq), x_scale=to_dev(xs), next_norm_w=to_dev(nw), next_q=nq,
-                            next_scale=ns, next_block_sumsq=nss)
+                            next_scale=ns, next_block_sumsq=nss, M=M)
     torch.cuda.synchronize()
     yh = y.cpu().numpy()
     assert max_abs_rel(yh, res + cpu_gemv(x1, W1, s1)) < 1e-3
     # what the producer emitted, against the rule applied to the y it wrote
     ref_q, ref_s = oracle.quantize_int8((yh * nw).astype(np.float32))
-    assert np.array_equal(nq.cpu().numpy().reshape(1, H), ref_q) and np.array_equal(ns.cpu().numpy().reshape(1, -1), ref_s)
-    ss = (yh.astype(np.float64) ** 2).reshape(-1, 16).sum(1)
+    assert np.array_equal(nq.cpu().numpy(), ref_q) and np.array_equal(ns.cpu().numpy(), ref_s)
+    ss = (yh.astype(np.float64) ** 2).reshape(M, -1, 16).sum(2)
     assert np.allclose(nss.cpu().numpy(), ss, rtol=1e-5)
     # the consumer
-    out = torch.full((1, N2), float("nan"), dtype=torch.float32, device="cuda")
-    k.gemv_w4a8_pending(out, None, W2d, s2d, H, N2, x_q=nq, x_scale=ns, x_block_sumsq=nss, eps=eps)
+    out = torch.full((M, N2), float("nan"), dtype=torch.float32, device="cuda")
+    k.gemv_w4a8_pending(out, None, W2d, s2d, H, N2, x_q=nq, x_scale=ns, x_block_sumsq=nss, eps=eps, M=M)
     ref = cpu_gemv(oracle.rmsnorm(yh, nw), W2, s2)
     assert max_abs_rel(out.cpu().numpy(), ref) < 1e-3
     # and against this library's fused-norm prologue on the same y
     out2 = torch.empty_like(out)
-    k.gemv_w4a8_decode(out2, 0, None, y, None, 0, to_dev(nw), eps, W2d, s2d, H, N2, 1)
+    k.gemv_w4a8_decode(out2, 0, None, y, None, 0, to_dev(nw), eps, W2d, s2d, H, N2, M)
     assert max_abs_rel(out.cpu().numpy(), out2.cpu().numpy()) < 1e-3
     assert k.device_status() == 0
