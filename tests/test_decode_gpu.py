@@ -12,6 +12,8 @@ from tests.util import max_abs_rel, to_dev
 pytestmark = pytest.mark.gpu
 
 SMALL = ModelShape("small", layers=2, hidden=256, inter=416, n_q_heads=4, n_kv_heads=2, head_dim=128, vocab=1003)
+# four query heads per kv head: the fused attention form with quantized output, and at batch 1 the norm-pending hand-over
+SMALL_GQ4 = ModelShape("small-gq4", layers=2, hidden=256, inter=416, n_q_heads=8, n_kv_heads=2, head_dim=128, vocab=1003)
 
 
 class HostWeights:
@@ -34,20 +36,21 @@ def cpu_gemv(x, W, sc16):
     return oracle.gemv_w4a8_f64(q, s, W, sc16).astype(np.float32)
 
 
-@pytest.mark.parametrize("M", [3, 16])
-def test_decode_step_matches_cpu_chain(cuda, M):
-    """Batch 3 runs the dp4a GEMV kernel, batch 16 the mma.sync one."""
+@pytest.mark.parametrize("M,s", [(3, SMALL), (16, SMALL), (1, SMALL_GQ4), (3, SMALL_GQ4), (8, SMALL_GQ4)])
+def test_decode_step_matches_cpu_chain(cuda, M, s):
+    """Batch 3 runs the dp4a GEMV kernel, batch 8 and 16 the mma.sync one; with four query heads per kv head the fused
+    attention form, and at batch 1 the norm-pending hand-over between the GEMVs."""
     import torch
 
     from blackwell_b200.decode import ROPE_BASE, DecodeEngine
 
-    s, max_seq, ctx = SMALL, 96, 40
+    max_seq, ctx = 96, 40
     hw = HostWeights()
     eng = DecodeEngine(s, M, max_seq, cuda, seed=5, host_weights=hw)
     eng.fill_cache(ctx)
-    pos0 = np.array([ctx - 1, ctx - 5, 3] + [(5 * i) % ctx for i in range(M - 3)], np.int32)
+    pos0 = np.array(([ctx - 1, ctx - 5, 3] + [(5 * i) % ctx for i in range(M - 3)])[:M], np.int32)
     eng.pos.copy_(torch.from_numpy(pos0))
-    toks = np.array([7, 1002, 500] + [(91 * i + 13) % s.vocab for i in range(M - 3)], np.int32)
+    toks = np.array(([7, 1002, 500] + [(91 * i + 13) % s.vocab for i in range(M - 3)])[:M], np.int32)
     eng.set_tokens(toks)
     Kc = eng.kc.cpu().numpy().copy()
     Vc = eng.vc.cpu().numpy().copy()
